@@ -43,7 +43,7 @@ class KVGroup:
         # zero-filled once: a page's unwritten rows are never selected by a mask, but they
         # are multiplied by zero weights, and 0 * NaN would not be 0
         self.k = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_entries)]
-        self.v = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_entries)]
+        self.v = [None if need.keys_only else torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_entries)]
         self.table_host = torch.zeros((n_slots, self.table_stride), dtype=torch.int32)
         self.table_dev = torch.zeros((n_slots, self.table_stride), dtype=torch.int32, device=device)
         self._slot_pages: Dict[int, List[int]] = {}
@@ -106,4 +106,4 @@ class KVGroup:
 
     def bytes_per_token(self) -> int:
         e = self.k[0].element_size()
-        return 2 * self.n_entries * self.need.n_kv_heads * self.need.head_dim * e
+        return (1 if self.need.keys_only else 2) * self.n_entries * self.need.n_kv_heads * self.need.head_dim * e

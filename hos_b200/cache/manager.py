@@ -40,7 +40,7 @@ class CacheManager:
     def __init__(self, kv_needs: Sequence[Optional[KVNeed]], cache_from: Sequence[Optional[int]],
                  state_needs: Sequence[Sequence[StateNeed]], max_tokens: int, max_seq_len: int,
                  dtype: torch.dtype, device: torch.device, max_slots: Optional[int] = None,
-                 chunk_tokens: int = 1):
+                 chunk_tokens: int = 1, embedding_needs: Sequence[StateNeed] = ()):
         """kv_needs[i], cache_from[i], state_needs[i] describe entry i of the run order.
         `chunk_tokens`: the most tokens one step adds to a sequence that is under way (a window
         group's ring is made long enough for it; longer additions are cut by the step function)."""
@@ -86,6 +86,10 @@ class CacheManager:
             state = {s.name: torch.zeros((self.n_slots,) + tuple(s.shape), dtype=s.dtype,
                                          device=self.device) for s in state_needs[i]}
             self.stores.append(CallStore(kv, owns, state))
+        # what the embedding keeps per sequence (e.g. the previous token, for a table of token pairs)
+        self.embedding_store = CallStore(None, True, {
+            s.name: torch.zeros((self.n_slots,) + tuple(s.shape), dtype=s.dtype, device=self.device)
+            for s in embedding_needs})
         self.record = torch.zeros((self.n_slots, RECORD_WORDS), dtype=torch.int32, device=self.device)
         self.recent = torch.zeros((self.n_slots, RECENT_TOKENS), dtype=torch.int32, device=self.device)
 
@@ -118,11 +122,30 @@ class CacheManager:
                 end += 1
             lo, hi = ordered[at], ordered[end - 1] + 1
             self.record[lo:hi].zero_()
-            for st in self.stores:
-                for t in st.state.values():
-                    t[lo:hi].zero_()
+            for t in self.state_tensors():
+                t[lo:hi].zero_()
             at = end
         return out
+
+    def state_tensors(self) -> List[torch.Tensor]:
+        """Every per-sequence state tensor of fixed size ([n_slots, ...]): the mixers' and the embedding's."""
+        return [t for st in self.stores + [self.embedding_store] for t in st.state.values()]
+
+    def snapshot_state(self, slots: torch.Tensor):
+        """Copies of the given slots' rows of every state tensor (None if there is no such state): a step that is
+        run once before it is captured and replayed must not move a recurrence on twice."""
+        tensors = self.state_tensors()
+        if not tensors:
+            return None
+        idx = slots.long()
+        return idx, [t.index_select(0, idx) for t in tensors]
+
+    def restore_state(self, snap) -> None:
+        if snap is None:
+            return
+        idx, rows = snap
+        for t, r in zip(self.state_tensors(), rows):
+            t.index_copy_(0, idx, r)
 
     def extend(self, slot: int, new_len: int) -> None:
         if slot not in self.lengths:

@@ -106,11 +106,13 @@ class PartSpec:
 class LayerSpec:
     """One layer: an arrangement (how norms, mixer, feed-forward and the residual
     stream are wired) and the parts it wires.  `norms` is keyed by the role names
-    the arrangement defines."""
+    the arrangement defines; `params` holds the arrangement's own constants (a factor on the
+    branches' sum, for instance)."""
     arrangement: str
     mixer: PartSpec
     feed_forward: PartSpec
     norms: Mapping[str, PartSpec]
+    params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -17,6 +17,9 @@ Libraries and what needs them:
               and for decoding over the paged cache
   gemm_tc     bfloat16 models: the tcgen05/TMA matrix product
   gemm_skinny bfloat16 models: the matrix product for up to 16 rows (decoding)
+  blocks      models built from the other kinds of block: the hashed token-pair embedding, the
+              parallel block's add-and-norms, attention over a latent cache, the matrix-state
+              recurrence, the routed feed-forward
 """
 from __future__ import annotations
 
@@ -43,6 +46,7 @@ _STATIC_LIBS: Dict[str, Tuple[List[str], List[str]]] = {
     "core": (["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "slot_state.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
+    "blocks": (["embed_pair.cu", "latent_attention.cu", "wkv.cu", "moe.cu"], []),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

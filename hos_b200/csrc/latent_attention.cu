@@ -1,0 +1,381 @@
+// Attention over a compressed (latent) key/value cache.
+//
+// Per position the cache keeps one row of D = R + P numbers shared by all heads: the latent c
+// (R numbers, RMS-normed) and one rotated key part (P numbers).  A head's key would be
+// [W_uk_h c | rotated part] and its value W_uv_h c; neither is ever formed.  The query side
+// absorbs W_uk instead:
+//     score_h(i, j) = scale * ( (W_uk_h^T q_h)[0:R] . c_j  +  rot(q_h)[R:D] . rot_key_j )
+// and the value projection is applied after the weighted sum of latents:
+//     out_h(i) = W_uv_h  sum_j p_h(i, j) c_j.
+// So every head reads the same D numbers per key (one key/value "head" of size D whose value is
+// its first R numbers).  Scores, softmax and the weighted sums are 32-bit FMA work whatever the
+// storage type is.  Mask: causal with an optional window of the last `window` keys.  Optional
+// sink: a learned number per head that joins the softmax's denominator as exp(sink), without a key
+// or a value and unscaled.
+//
+// Kernels: latent_prep (norm of c, rotations, cache write), latent_attn (keys from the step's own
+// rows for sequences that start at position 0, or from the paged cache), heads_product (the per-head
+// products W_uk_h^T q_h and W_uv_h o_h as one launch over all heads).
+#include "common.cuh"
+#include "kv_layout.cuh"
+
+namespace hos {
+
+// ---- latent_prep ---------------------------------------------------------------------------
+// proj[n] = [ q: H heads of (dq + P) | c_raw: R | key_rot_raw: P ].  Writes
+//   kc[n]     = [ rms(c_raw) * w_norm | rot(key_rot_raw) ]                (the row the cache keeps)
+//   q_lat[n][h][R : R + P] = rot(q_h[dq : dq + P])                        (32-bit)
+// and stores kc[n] at the token's place in the paged cache (rows of D, not permuted).
+// Rotation: the first rot_dims of the P numbers, pairs (2i, 2i + 1), angle = position * inv_freq[i].
+template <typename T>
+__global__ void latent_prep_kernel(const T* __restrict__ proj, int proj_stride, int H, int dq, int R, int P,
+                                   const float* __restrict__ w_norm, float eps, const float* __restrict__ inv_freq,
+                                   int rot_dims, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                                   const int* __restrict__ seq_slot, const int* __restrict__ seq_len_after,
+                                   T* __restrict__ kc, float* __restrict__ q_lat, T* __restrict__ k_pages,
+                                   const int* __restrict__ page_table, int table_stride, int ring_pages) {
+    pdl_enter();
+    extern __shared__ float2 sincos_tab[];      // [rot_dims / 2]
+    __shared__ float scratch[32];
+    const int n = blockIdx.x;
+    const int seq = token_seq[n];
+    if (seq < 0) return;
+    const int pos = token_pos[n], D = R + P, half = rot_dims >> 1;
+    int page = -1;
+    if (k_pages != nullptr && !(ring_pages > 0 && pos + ring_pages * kPageTokens < seq_len_after[seq])) {
+        const int lp = pos / kPageTokens;
+        page = page_table[(size_t)seq_slot[seq] * table_stride + (ring_pages > 0 ? lp % ring_pages : lp)];
+    }
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        sincos_tab[i] = make_float2(s, c);
+    }
+    const T* row = proj + (size_t)n * proj_stride;
+    const T* craw = row + (size_t)H * (dq + P);
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < R; d += blockDim.x) {
+        const float v = to_float(craw[d]);
+        ss = fmaf(v, v, ss);
+    }
+    const float rinv = rsqrtf(block_sum(ss, scratch) / (float)R + eps);      // (also orders sincos_tab)
+    T* out = kc + (size_t)n * D;
+    T* cached = page >= 0 ? k_pages + ((size_t)page * kPageTokens + pos % kPageTokens) * D : nullptr;
+    for (int d = threadIdx.x; d < R; d += blockDim.x) {
+        const T v = from_float<T>(to_float(craw[d]) * rinv * w_norm[d]);
+        out[d] = v;
+        if (cached) cached[d] = v;
+    }
+    // the shared rotated key part, then every head's rotated query part: items of one pair (or one
+    // unrotated number beyond rot_dims)
+    const int per = half + (P - rot_dims);
+    for (int it = threadIdx.x; it < (H + 1) * per; it += blockDim.x) {
+        const int who = it / per, j = it - who * per;       // who == H: the key
+        const T* src = who == H ? craw + R : row + (size_t)who * (dq + P) + dq;
+        float a, b = 0.f;
+        int d0;
+        const bool pair = j < half;
+        if (pair) {
+            d0 = 2 * j;
+            const float2 sc = sincos_tab[j];
+            const float u = to_float(src[d0]), v = to_float(src[d0 + 1]);
+            a = u * sc.y - v * sc.x;
+            b = v * sc.y + u * sc.x;
+        } else {
+            d0 = rot_dims + (j - half);
+            a = to_float(src[d0]);
+        }
+        if (who == H) {
+            const T ta = from_float<T>(a), tb = from_float<T>(b);
+            out[R + d0] = ta;
+            if (cached) cached[R + d0] = ta;
+            if (pair) {
+                out[R + d0 + 1] = tb;
+                if (cached) cached[R + d0 + 1] = tb;
+            }
+        } else {
+            float* q = q_lat + ((size_t)n * H + who) * D + R;
+            q[d0] = a;
+            if (pair) q[d0 + 1] = b;
+        }
+    }
+}
+
+// ---- latent_attn ---------------------------------------------------------------------------
+// One block per (row, group of kHG heads).  Keys come in tiles of kTK positions, each row brought
+// to shared memory as 32-bit numbers.  Scores: warp = head, lane = key.  Weighted sums: a thread
+// owns up to kNC columns of the latent for all heads of the group.
+constexpr int kHG = 8, kTK = 32, kNC = 4, kAttnThreads = 256;
+
+template <typename T, bool PAGED>
+__global__ void __launch_bounds__(kAttnThreads)
+latent_attn_kernel(const float* __restrict__ q_lat, const T* __restrict__ kc, const T* __restrict__ k_pages,
+                   const int* __restrict__ page_table, int table_stride, int ring_pages,
+                   const float* __restrict__ sink, float* __restrict__ o_lat, const int* __restrict__ token_pos,
+                   const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
+                   const int* __restrict__ seq_slot, int row0, int H, int R, int D, int Dq, int Dk, float scale,
+                   int window) {
+    pdl_enter();
+    extern __shared__ float smem[];
+    float* qs = smem;                          // [kHG][Dq]
+    float* ks = qs + kHG * Dq;                 // [kTK][Dk]
+    float* ps = ks + kTK * Dk;                 // [kTK][kHG] weights of the tile
+    float* alpha = ps + kTK * kHG;             // [kHG] what the running sums are scaled by
+    float* denom = alpha + kHG;                // [kHG]
+    __shared__ int key_row[kTK];               // where each key of the tile lies (-1: none)
+    const int n = row0 + blockIdx.x, h0 = blockIdx.y * kHG;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nh = min(kHG, H - h0);
+    const int seq = token_seq[n];
+    if (seq < 0) {                             // padding: zeros, so that what follows stays finite
+        for (int i = tid; i < nh * R; i += kAttnThreads) o_lat[((size_t)n * H + h0) * R + i] = 0.f;
+        return;
+    }
+    const int pos = token_pos[n];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    for (int i = tid; i < kHG * Dq; i += kAttnThreads) {
+        const int h = i / Dq, d = i - h * Dq;
+        qs[i] = (h < nh && d < D) ? q_lat[((size_t)n * H + h0 + h) * D + d] : 0.f;
+    }
+    const int seq_first = PAGED ? 0 : cu_seqlens[seq];
+    const int* table = PAGED ? page_table + (size_t)seq_slot[seq] * table_stride : nullptr;
+    float m_run = -INFINITY, l_run = 0.f;      // of head `warp` (kept by every lane of the warp)
+    if (warp < nh && sink != nullptr) {
+        m_run = sink[h0 + warp];
+        l_run = 1.f;
+    }
+    float acc[kNC][kHG];
+#pragma unroll
+    for (int c = 0; c < kNC; ++c)
+#pragma unroll
+        for (int h = 0; h < kHG; ++h) acc[c][h] = 0.f;
+
+    for (int p0 = lo; p0 <= pos; p0 += kTK) {
+        __syncthreads();                       // the tile before is used up (and qs is written)
+        if (tid < kTK) {
+            const int p = p0 + tid;
+            int r = -1;
+            if (p <= pos) {
+                if (PAGED) {
+                    const int lp = p / kPageTokens;
+                    r = table[ring_pages > 0 ? lp % ring_pages : lp] * kPageTokens + p % kPageTokens;
+                } else {
+                    r = seq_first + p;
+                }
+            }
+            key_row[tid] = r;
+        }
+        __syncthreads();
+        for (int j = warp; j < kTK; j += kAttnThreads / 32) {
+            const int r = key_row[j];
+            float* dst = ks + j * Dk;
+            if (r < 0) {
+                for (int d = lane; d < Dk; d += 32) dst[d] = 0.f;
+            } else {
+                const T* src = (PAGED ? k_pages : kc) + (size_t)r * D;
+                for (int d = lane; d < Dk; d += 32) dst[d] = d < D ? to_float(src[d]) : 0.f;
+            }
+        }
+        __syncthreads();
+        if (warp < nh) {
+            const float4* qv = reinterpret_cast<const float4*>(qs + warp * Dq);
+            const float4* kv = reinterpret_cast<const float4*>(ks + lane * Dk);
+            float s = 0.f;
+            for (int i = 0; i < (Dq >> 2); ++i) {
+                const float4 a = qv[i], b = kv[i];
+                s = fmaf(a.x, b.x, s);
+                s = fmaf(a.y, b.y, s);
+                s = fmaf(a.z, b.z, s);
+                s = fmaf(a.w, b.w, s);
+            }
+            const bool live = key_row[lane] >= 0;
+            s = live ? s * scale : -INFINITY;
+            const float m_new = fmaxf(m_run, warp_max(s));        // finite: a tile's first key is live
+            const float p = live ? expf(s - m_new) : 0.f;
+            const float a = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
+            l_run = fmaf(l_run, a, warp_sum(p));
+            m_run = m_new;
+            ps[lane * kHG + warp] = p;
+            if (lane == 0) alpha[warp] = a;
+        } else if (warp < kHG) {
+            ps[lane * kHG + warp] = 0.f;
+            if (lane == 0) alpha[warp] = 0.f;
+        }
+        __syncthreads();
+        float al[kHG];
+#pragma unroll
+        for (int h = 0; h < kHG; ++h) al[h] = alpha[h];
+#pragma unroll
+        for (int c = 0; c < kNC; ++c) {
+            const int col = tid + c * kAttnThreads;
+            if (col >= R) break;
+#pragma unroll
+            for (int h = 0; h < kHG; ++h) acc[c][h] *= al[h];
+            for (int j = 0; j < kTK; ++j) {
+                const float v = ks[j * Dk + col];
+                const float4 pa = *reinterpret_cast<const float4*>(ps + j * kHG);
+                const float4 pb = *reinterpret_cast<const float4*>(ps + j * kHG + 4);
+                acc[c][0] = fmaf(pa.x, v, acc[c][0]);
+                acc[c][1] = fmaf(pa.y, v, acc[c][1]);
+                acc[c][2] = fmaf(pa.z, v, acc[c][2]);
+                acc[c][3] = fmaf(pa.w, v, acc[c][3]);
+                acc[c][4] = fmaf(pb.x, v, acc[c][4]);
+                acc[c][5] = fmaf(pb.y, v, acc[c][5]);
+                acc[c][6] = fmaf(pb.z, v, acc[c][6]);
+                acc[c][7] = fmaf(pb.w, v, acc[c][7]);
+            }
+        }
+    }
+    if (warp < kHG && lane == 0) denom[warp] = warp < nh ? l_run : 1.f;
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < kNC; ++c) {
+        const int col = tid + c * kAttnThreads;
+        if (col >= R) break;
+#pragma unroll
+        for (int h = 0; h < kHG; ++h)
+            if (h < nh) o_lat[((size_t)n * H + h0 + h) * R + col] = acc[c][h] / denom[h];
+    }
+}
+
+// ---- heads_product -------------------------------------------------------------------------
+// out[n, h, o] = sum_i W[h][o][i] * in[n, h, i] for every head h in one launch (blockIdx.z = head):
+// 64 x 64 tiles, 32-bit FMA.  Row and head strides of `in` and `out` are given in elements.
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+heads_product_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __restrict__ out, int M, int N, int K,
+                     int lda, int a_head, int w_head, int ldo, int o_head) {
+    pdl_enter();
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN, h = blockIdx.z;
+    A += (size_t)h * a_head;
+    W += (size_t)h * w_head;
+    out += (size_t)h * o_head;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int e = threadIdx.x; e < BM * BK; e += 256) {
+            const int r = e >> 4, kk = e & 15;
+            const int m = m0 + r, k = k0 + kk, nn = n0 + r;
+            As[kk][r] = (m < M && k < K) ? to_float(A[(size_t)m * lda + k]) : 0.f;
+            Ws[kk][r] = (nn < N && k < K) ? to_float(W[(size_t)nn * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int nn = n0 + tx * 4 + j;
+            if (nn < N) out[(size_t)m * ldo + nn] = from_float<TO>(acc[i][j]);
+        }
+    }
+}
+
+template <typename T>
+static int launch_prep(const void* proj, int proj_stride, int H, int dq, int R, int P, const float* w_norm, float eps,
+                       const float* inv_freq, int rot_dims, const int* token_pos, const int* token_seq,
+                       const int* seq_slot, const int* seq_len_after, void* kc, float* q_lat, void* k_pages,
+                       const int* page_table, int table_stride, int ring_pages, int N, cudaStream_t stream) {
+    launch_pdl(latent_prep_kernel<T>, dim3(N), dim3(128), (size_t)(rot_dims / 2 + 1) * sizeof(float2), stream,
+               (const T*)proj, proj_stride, H, dq, R, P, w_norm, eps, inv_freq, rot_dims, token_pos, token_seq, seq_slot,
+               seq_len_after, (T*)kc, q_lat, (T*)k_pages, page_table, table_stride, ring_pages);
+    return check_launch("latent_prep");
+}
+
+template <typename T, bool PAGED>
+static int launch_attn(const float* q_lat, const void* kc, const void* k_pages, const int* page_table, int table_stride,
+                       int ring_pages, const float* sink, float* o_lat, const int* token_pos, const int* token_seq,
+                       const int* cu_seqlens, const int* seq_slot, int row0, int rows, int H, int R, int D, float scale,
+                       int window, cudaStream_t stream) {
+    const int Dq = (D + 3) / 4 * 4;
+    const int Dk = 4 * (((D + 3) / 4) | 1);        // rows of 16-byte groups, an odd number of them: no bank conflicts
+    const size_t smem = (size_t)(kHG * Dq + kTK * Dk + kTK * kHG + 2 * kHG) * sizeof(float);
+    if (smem > 200 * 1024) HOS_REFUSE("latent_attn: rows of %d numbers do not fit a block's shared memory", D);
+    auto kernel = latent_attn_kernel<T, PAGED>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(kernel, dim3(rows, (H + kHG - 1) / kHG), dim3(kAttnThreads), smem, stream, q_lat, (const T*)kc,
+               (const T*)k_pages, page_table, table_stride, ring_pages, sink, o_lat, token_pos, token_seq, cu_seqlens,
+               seq_slot, row0, H, R, D, Dq, Dk, scale, window);
+    return check_launch("latent_attn");
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+extern "C" int hos_latent_prep(const void* proj, int dtype, int proj_stride, int H, int dq, int R, int P,
+                               const float* w_norm, float eps, const float* inv_freq, int rot_dims,
+                               const int* token_pos, const int* token_seq, const int* seq_slot,
+                               const int* seq_len_after, void* kc, float* q_lat, void* k_pages,
+                               const int* page_table, int table_stride, int ring_pages, int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (rot_dims < 0 || rot_dims > P || (rot_dims & 1)) HOS_REFUSE("latent_prep: %d rotated of %d numbers", rot_dims, P);
+    if (dtype == kBF16)
+        return launch_prep<bf16>(proj, proj_stride, H, dq, R, P, w_norm, eps, inv_freq, rot_dims, token_pos, token_seq,
+                                 seq_slot, seq_len_after, kc, q_lat, k_pages, page_table, table_stride, ring_pages, N, stream);
+    if (dtype == kF32)
+        return launch_prep<float>(proj, proj_stride, H, dq, R, P, w_norm, eps, inv_freq, rot_dims, token_pos, token_seq,
+                                  seq_slot, seq_len_after, kc, q_lat, k_pages, page_table, table_stride, ring_pages, N, stream);
+    HOS_REFUSE("latent_prep: unknown dtype %d", dtype);
+}
+
+// Rows row0 .. row0 + rows - 1 of the step.  paged = 0: keys are the step's own rows `kc` (sequences
+// that start at position 0); paged = 1: keys from `k_pages` through the page table.
+extern "C" int hos_latent_attn(int dtype, int paged, const float* q_lat, const void* kc, const void* k_pages,
+                               const int* page_table, int table_stride, int ring_pages, const float* sink,
+                               float* o_lat, const int* token_pos, const int* token_seq, const int* cu_seqlens,
+                               const int* seq_slot, int row0, int rows, int H, int R, int D, float scale, int window,
+                               cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (R > kNC * kAttnThreads) HOS_REFUSE("latent_attn: a latent of %d numbers is more than %d", R, kNC * kAttnThreads);
+    if (R > D) HOS_REFUSE("latent_attn: the latent (%d) is longer than the row (%d)", R, D);
+#define HOS_GO(T, PG) return launch_attn<T, PG>(q_lat, kc, k_pages, page_table, table_stride, ring_pages, sink, o_lat, \
+                                                 token_pos, token_seq, cu_seqlens, seq_slot, row0, rows, H, R, D, scale, window, stream)
+    if (dtype == kBF16 && paged) HOS_GO(bf16, true);
+    if (dtype == kBF16) HOS_GO(bf16, false);
+    if (dtype == kF32 && paged) HOS_GO(float, true);
+    if (dtype == kF32) HOS_GO(float, false);
+#undef HOS_GO
+    HOS_REFUSE("latent_attn: unknown dtype %d", dtype);
+}
+
+// out[m, h, 0:N] = W[h] (N x K, rows contiguous) . in[m, h, 0:K]; strides in elements.
+extern "C" int hos_heads_product(const void* in, int in_dtype, const void* W, int w_dtype, void* out, int out_dtype,
+                                 int M, int N, int K, int heads, int lda, int a_head, int ldo, int o_head,
+                                 cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || heads <= 0) return 0;
+    if (K <= 0) HOS_REFUSE("heads_product: K must be positive");
+    dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
+    if (grid.y > 65535 || grid.z > 65535) HOS_REFUSE("heads_product: too many rows or heads for one launch");
+#define HOS_CASE(da, dw, dout, TA, TW, TO)                                                            \
+    if (in_dtype == da && w_dtype == dw && out_dtype == dout) {                                       \
+        launch_pdl(heads_product_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, (const TA*)in,       \
+                   (const TW*)W, (TO*)out, M, N, K, lda, a_head, N * K, ldo, o_head);                 \
+        return check_launch("heads_product");                                                         \
+    }
+    HOS_CASE(kF32, kF32, kF32, float, float, float)
+    HOS_CASE(kBF16, kBF16, kF32, bf16, bf16, float)
+    HOS_CASE(kF32, kBF16, kBF16, float, bf16, bf16)
+    HOS_CASE(kF32, kBF16, kF32, float, bf16, float)
+    HOS_CASE(kBF16, kBF16, kBF16, bf16, bf16, bf16)
+#undef HOS_CASE
+    HOS_REFUSE("heads_product: no kernel for dtypes in=%d W=%d out=%d", in_dtype, w_dtype, out_dtype);
+}

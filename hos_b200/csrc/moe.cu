@@ -1,0 +1,368 @@
+// A routed feed-forward (mixture of experts) whose whole step stays on the device.
+//
+//   route     per row: router logits in 32-bit, softmax over all outputs, the `top` largest of
+//             (score + correction) chosen, each weighted by its plain score (not renormalised).
+//             The last `n_identity` router outputs are experts without tensors: their output is
+//             the row itself.
+//   align     the chosen (row, choice) pairs listed expert by expert, each expert's list padded to
+//             whole tiles of kTile rows, and the expert of every tile.
+//   gate_up   per tile, the expert's gate and up products of the listed rows and the activation
+//             y = g' * sigmoid(alpha * g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
+//             (limit <= 0: no clamp).
+//   down      per tile, the expert's down product, times the pair's weight, to the pair's own row
+//             of a 32-bit buffer.
+//   combine   per row, the sum of its pairs' rows in the order of the choices, identity experts added
+//             as weight * row.
+// The grid of the tiled kernels is the most tiles the step can have; tiles beyond the real ones
+// leave at once, so nothing depends on the host knowing the counts.  Products accumulate in 32-bit;
+// a warp whose rows of a tile are all padding skips the arithmetic.
+#include "common.cuh"
+
+namespace hos {
+
+constexpr int kTile = 64;
+
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router,
+                                 const float* __restrict__ correction, const int* __restrict__ token_seq,
+                                 int* __restrict__ choice, float* __restrict__ weight, int D, int n_out, int top) {
+    pdl_enter();
+    extern __shared__ float z[];               // [n_out] scores, then [n_out] taken flags
+    float* taken = z + n_out;
+    const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    if (token_seq[n] < 0) {
+        for (int k = threadIdx.x; k < top; k += blockDim.x) {
+            choice[(size_t)n * top + k] = -1;
+            weight[(size_t)n * top + k] = 0.f;
+        }
+        return;
+    }
+    const T* row = h + (size_t)n * D;
+    for (int e = warp; e < n_out; e += nwarps) {
+        const float* w = router + (size_t)e * D;
+        float s = 0.f;
+        for (int d = lane; d < D; d += 32) s = fmaf(to_float(row[d]), w[d], s);
+        s = warp_sum(s);
+        if (lane == 0) {
+            z[e] = s;
+            taken[e] = 0.f;
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float m = -INFINITY;
+    for (int e = lane; e < n_out; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < n_out; e += 32) {
+        const float p = expf(z[e] - m);
+        z[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < n_out; e += 32) z[e] = z[e] / sum;
+    __syncwarp();
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < n_out; e += 32) {
+            if (taken[e] != 0.f) continue;
+            const float c = z[e] + (correction ? correction[e] : 0.f);
+            if (c > best || (c == best && e < arg)) {
+                best = c;
+                arg = e;
+            }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) {
+                best = ob;
+                arg = oa;
+            }
+        }
+        if (lane == 0) {
+            const bool ok = arg != 0x7fffffff;
+            choice[(size_t)n * top + k] = ok ? arg : -1;
+            weight[(size_t)n * top + k] = ok ? z[arg] : 0.f;
+            if (ok) taken[arg] = 1.f;
+        }
+        __syncwarp();
+    }
+}
+
+// One block.  listed: [cap] pair ids (row * top + choice) expert by expert, -1 where a tile is padded;
+// tile_expert: [max_tiles], -1 beyond the real tiles.
+__global__ void moe_align_kernel(const int* __restrict__ choice, int n_pairs, int n_experts, int* __restrict__ listed,
+                                 int cap, int* __restrict__ tile_expert, int max_tiles) {
+    pdl_enter();
+    extern __shared__ int sh[];                // count[n_experts], start[n_experts + 1], cursor[n_experts]
+    int* count = sh;
+    int* start = count + n_experts;
+    int* cursor = start + n_experts + 1;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = cursor[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = choice[i];
+        if (e >= 0 && e < n_experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            start[e] = at;
+            const int tiles = (count[e] + kTile - 1) / kTile;
+            for (int t = 0; t < tiles; ++t)
+                if (at / kTile + t < max_tiles) tile_expert[at / kTile + t] = e;
+            at += tiles * kTile;
+        }
+        start[n_experts] = at;
+        for (int t = at / kTile; t < max_tiles; ++t) tile_expert[t] = -1;
+    }
+    __syncthreads();
+    const int used = min(start[n_experts], cap);
+    for (int i = threadIdx.x; i < used; i += blockDim.x) listed[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = choice[i];
+        if (e >= 0 && e < n_experts) {
+            const int p = start[e] + atomicAdd(&cursor[e], 1);
+            if (p < cap) listed[p] = i;
+        }
+    }
+}
+
+// y[listed position][F] = act(gate, up) of the listed rows; W: [experts][2F][D], gate rows then up rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ W, const int* __restrict__ listed,
+                   const int* __restrict__ tile_expert, T* __restrict__ y, int D, int F, int top, float limit,
+                   float alpha) {
+    pdl_enter();
+    constexpr int BK = 16;
+    __shared__ float As[BK][kTile + 4];
+    __shared__ float Gs[BK][kTile + 4];
+    __shared__ float Us[BK][kTile + 4];
+    __shared__ int rows[kTile];
+    const int tile = blockIdx.y, e = tile_expert[tile];
+    if (e < 0) return;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4, n0 = blockIdx.x * kTile;
+    if (threadIdx.x < kTile) {
+        const int id = listed[tile * kTile + threadIdx.x];
+        rows[threadIdx.x] = id >= 0 ? id / top : -1;
+    }
+    __syncthreads();
+    const int warp_row0 = (threadIdx.x >> 5) * 8;          // a warp's threads hold rows warp_row0 .. +7
+    bool busy = false;
+    for (int i = 0; i < 8; ++i) busy = busy || rows[warp_row0 + i] >= 0;
+    const T* Wg = W + (size_t)e * 2 * F * D;
+    const T* Wu = Wg + (size_t)F * D;
+    float acc_g[4][4] = {}, acc_u[4][4] = {};
+    for (int k0 = 0; k0 < D; k0 += BK) {
+        for (int x = threadIdx.x; x < kTile * BK; x += 256) {
+            const int r = x >> 4, kk = x & 15, k = k0 + kk, n = n0 + r;
+            const int src = rows[r];
+            As[kk][r] = (src >= 0 && k < D) ? to_float(h[(size_t)src * D + k]) : 0.f;
+            const bool in = n < F && k < D;
+            Gs[kk][r] = in ? to_float(Wg[(size_t)n * D + k]) : 0.f;
+            Us[kk][r] = in ? to_float(Wu[(size_t)n * D + k]) : 0.f;
+        }
+        __syncthreads();
+        if (busy) {
+#pragma unroll
+            for (int kk = 0; kk < BK; ++kk) {
+                float a[4], g[4], u[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    g[j] = Gs[kk][tx * 4 + j];
+                    u[j] = Us[kk][tx * 4 + j];
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc_g[i][j] = fmaf(a[i], g[j], acc_g[i][j]);
+                        acc_u[i][j] = fmaf(a[i], u[j], acc_u[i][j]);
+                    }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (rows[r] < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= F) continue;
+            float g = acc_g[i][j], u = acc_u[i][j];
+            if (limit > 0.f) {
+                g = fminf(g, limit);
+                u = fminf(fmaxf(u, -limit), limit);
+            }
+            const float v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+            y[(size_t)(tile * kTile + r) * F + n] = from_float<T>(v);
+        }
+    }
+}
+
+// pair_out[pair id][D] = weight[pair id] * (W_down[e] . y[listed position]); W: [experts][D][F].
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const T* __restrict__ y, const T* __restrict__ W, const int* __restrict__ listed,
+                const int* __restrict__ tile_expert, const float* __restrict__ weight, float* __restrict__ pair_out,
+                int D, int F) {
+    pdl_enter();
+    constexpr int BK = 16;
+    __shared__ float As[BK][kTile + 4];
+    __shared__ float Ws[BK][kTile + 4];
+    __shared__ int ids[kTile];
+    const int tile = blockIdx.y, e = tile_expert[tile];
+    if (e < 0) return;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4, n0 = blockIdx.x * kTile;
+    if (threadIdx.x < kTile) ids[threadIdx.x] = listed[tile * kTile + threadIdx.x];
+    __syncthreads();
+    const int warp_row0 = (threadIdx.x >> 5) * 8;
+    bool busy = false;
+    for (int i = 0; i < 8; ++i) busy = busy || ids[warp_row0 + i] >= 0;
+    const T* Wd = W + (size_t)e * D * F;
+    const T* A = y + (size_t)tile * kTile * F;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < F; k0 += BK) {
+        for (int x = threadIdx.x; x < kTile * BK; x += 256) {
+            const int r = x >> 4, kk = x & 15, k = k0 + kk, n = n0 + r;
+            As[kk][r] = (ids[r] >= 0 && k < F) ? to_float(A[(size_t)r * F + k]) : 0.f;
+            Ws[kk][r] = (n < D && k < F) ? to_float(Wd[(size_t)n * F + k]) : 0.f;
+        }
+        __syncthreads();
+        if (busy) {
+#pragma unroll
+            for (int kk = 0; kk < BK; ++kk) {
+                float a[4], w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int id = ids[ty * 4 + i];
+        if (id < 0) continue;
+        const float wt = weight[id];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < D) pair_out[(size_t)id * D + n] = acc[i][j] * wt;
+        }
+    }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ choice,
+                                   const float* __restrict__ weight, const T* __restrict__ h, float* __restrict__ out,
+                                   int D, int top, int n_experts) {
+    pdl_enter();
+    const int n = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const size_t id = (size_t)n * top + k;
+            const int e = choice[id];
+            if (e < 0) continue;
+            s += e < n_experts ? pair_out[id * D + d] : weight[id] * to_float(h[(size_t)n * D + d]);
+        }
+        out[(size_t)n * D + d] = s;
+    }
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+extern "C" int hos_moe_tile_rows() { return kTile; }
+
+extern "C" int hos_moe_route(const void* h, int dtype, const float* router, const float* correction,
+                             const int* token_seq, int* choice, float* weight, int N, int D, int n_out, int top,
+                             cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (top <= 0 || top > n_out) HOS_REFUSE("moe_route: %d of %d router outputs cannot be chosen", top, n_out);
+    const size_t smem = (size_t)2 * n_out * sizeof(float);
+    if (smem > 48 * 1024) HOS_REFUSE("moe_route: %d router outputs are more than a block's shared memory holds", n_out);
+    if (dtype == kBF16)
+        launch_pdl(moe_route_kernel<bf16>, dim3(N), dim3(128), smem, stream, (const bf16*)h, router, correction, token_seq,
+                   choice, weight, D, n_out, top);
+    else if (dtype == kF32)
+        launch_pdl(moe_route_kernel<float>, dim3(N), dim3(128), smem, stream, (const float*)h, router, correction, token_seq,
+                   choice, weight, D, n_out, top);
+    else
+        HOS_REFUSE("moe_route: unknown dtype %d", dtype);
+    return check_launch("moe_route");
+}
+
+extern "C" int hos_moe_align(const int* choice, int n_pairs, int n_experts, int* listed, int cap, int* tile_expert,
+                             int max_tiles, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    const size_t smem = (size_t)(3 * n_experts + 1) * sizeof(int);
+    if (smem > 48 * 1024) HOS_REFUSE("moe_align: %d experts are more than a block's shared memory holds", n_experts);
+    launch_pdl(moe_align_kernel, dim3(1), dim3(1024), smem, stream, choice, n_pairs, n_experts, listed, cap, tile_expert,
+               max_tiles);
+    return check_launch("moe_align");
+}
+
+extern "C" int hos_moe_gate_up(const void* h, const void* W, int dtype, const int* listed, const int* tile_expert,
+                               void* y, int max_tiles, int D, int F, int top, float limit, float alpha,
+                               cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    dim3 grid((F + kTile - 1) / kTile, max_tiles);
+    if (grid.y > 65535) HOS_REFUSE("moe_gate_up: %d tiles are more than one launch takes", max_tiles);
+    if (dtype == kBF16)
+        launch_pdl(moe_gate_up_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, (const bf16*)W, listed, tile_expert,
+                   (bf16*)y, D, F, top, limit, alpha);
+    else if (dtype == kF32)
+        launch_pdl(moe_gate_up_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, (const float*)W, listed,
+                   tile_expert, (float*)y, D, F, top, limit, alpha);
+    else
+        HOS_REFUSE("moe_gate_up: unknown dtype %d", dtype);
+    return check_launch("moe_gate_up");
+}
+
+extern "C" int hos_moe_down(const void* y, const void* W, int dtype, const int* listed, const int* tile_expert,
+                            const float* weight, float* pair_out, int max_tiles, int D, int F, cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    dim3 grid((D + kTile - 1) / kTile, max_tiles);
+    if (grid.y > 65535) HOS_REFUSE("moe_down: %d tiles are more than one launch takes", max_tiles);
+    if (dtype == kBF16)
+        launch_pdl(moe_down_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)y, (const bf16*)W, listed, tile_expert,
+                   weight, pair_out, D, F);
+    else if (dtype == kF32)
+        launch_pdl(moe_down_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, (const float*)W, listed, tile_expert,
+                   weight, pair_out, D, F);
+    else
+        HOS_REFUSE("moe_down: unknown dtype %d", dtype);
+    return check_launch("moe_down");
+}
+
+extern "C" int hos_moe_combine(const float* pair_out, const int* choice, const float* weight, const void* h, int dtype,
+                               float* out, int N, int D, int top, int n_experts, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (dtype == kBF16)
+        launch_pdl(moe_combine_kernel<bf16>, dim3(N), dim3(256), 0, stream, pair_out, choice, weight, (const bf16*)h, out, D,
+                   top, n_experts);
+    else if (dtype == kF32)
+        launch_pdl(moe_combine_kernel<float>, dim3(N), dim3(256), 0, stream, pair_out, choice, weight, (const float*)h, out,
+                   D, top, n_experts);
+    else
+        HOS_REFUSE("moe_combine: unknown dtype %d", dtype);
+    return check_launch("moe_combine");
+}

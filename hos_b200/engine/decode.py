@@ -234,11 +234,13 @@ class DecodeSession:
             return prog
         c = self.runner.cache
         keep = (c.record.clone(), c.recent.clone())
+        state = c.snapshot_state(self.slot[: self.n_live])      # a recurrence must not be moved on twice
         before = ops.launch_count
         out = fn()
         self.launches_per_step = ops.launch_count - before
         c.record.copy_(keep[0])
         c.recent.copy_(keep[1])
+        c.restore_state(state)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         # nothing but this thread's own launches may touch the capture: no collection of old
@@ -446,7 +448,10 @@ class PromptSession:
             self.logits = self._forward()
             return self.logits[: self.n_live]
         if not self._ready:
+            c = self.runner.cache
+            state = c.snapshot_state(self.slot[: self.n_live])      # a recurrence must not be moved on twice
             self.logits = self._forward()       # first-use set-up of kernels must not happen inside a capture
+            c.restore_state(state)
             torch.cuda.synchronize()
             self._graph = torch.cuda.CUDAGraph()
             gc_was_on = gc.isenabled()

@@ -60,7 +60,7 @@ class Model:
             state_needs.append(mixer.state_needs())
         return CacheManager(kv_needs, cache_from, state_needs, max_tokens,
                             max_seq_len or self.plan.max_positions, self.rt.dtype, self.rt.device,
-                            max_slots, chunk_tokens)
+                            max_slots, chunk_tokens, self.embedding.state_needs())
 
     def hidden(self, step: StepInfo, cache: CacheManager, tap: Optional[list] = None) -> torch.Tensor:
         """The residual stream after the last entry of the run order, float32 [N, width].  With `tap`
@@ -72,7 +72,10 @@ class Model:
     def _run_layers(self, step: StepInfo, cache: CacheManager, tap: Optional[list], last_norm):
         """(x, h): the residual stream after the last entry of the run order and, if `last_norm` is given, that
         norm of it, which comes out of the last layer's last kernel where the arrangement hands norms on."""
-        x = self.embedding.forward(step.tokens, step)
+        if cache.embedding_store.state:
+            x = self.embedding.forward(step.tokens, step, cache.embedding_store)
+        else:
+            x = self.embedding.forward(step.tokens, step)
         if tap is not None:
             tap.append(x.clone())
         h = None

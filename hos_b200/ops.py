@@ -492,3 +492,178 @@ def slot_write(record, slots, values, word_mask: int) -> None:
 def decode_advance(tokens, token_pos, seq_len_after, token_seq, sampled) -> None:
     core().call("hos_decode_advance", _ptr(tokens), _ptr(token_pos), _ptr(seq_len_after), _ptr(token_seq),
                 _ptr(sampled), tokens.shape[0], _stream())
+
+
+# ---- the other kinds of block (csrc/embed_pair.cu, latent_attention.cu, wkv.cu, moe.cu) ------
+_blocks: Optional[Library] = None
+
+
+def blocks() -> Library:
+    global _blocks
+    if _blocks is None:
+        _blocks = Library("blocks")
+    return _blocks
+
+
+def embed_pair(step, prev_token: torch.Tensor, table: torch.Tensor, pair_table: torch.Tensor, buckets: int,
+               mul_prev: int, mul_cur: int, out: torch.Tensor) -> None:
+    """out[n] = table[token] + pair_table[(previous * mul_prev + token * mul_cur) % buckets], row `buckets`
+    for a sequence's first token; the previous token of a continuing sequence's first row is
+    prev_token[slot].  `step`: a StepInfo (device arrays)."""
+    _check(out, "embedding output", torch.float32, 2)
+    _check(prev_token, "previous tokens", torch.int32, 1)
+    n, d = out.shape
+    if table.dtype != pair_table.dtype or table.shape[1] != d or pair_table.shape != (buckets + 1, d):
+        raise KernelError("embed_pair: the tables do not fit each other or the output")
+    blocks().call("hos_embed_pair", _ptr(step.tokens), _ptr(step.token_pos), _ptr(step.token_seq),
+                  _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(prev_token), _ptr(table), _ptr(pair_table),
+                  dtype_code(table.dtype), int(buckets), int(mul_prev), int(mul_cur), _ptr(out), n, d, _stream())
+
+
+def keep_last_token(step, prev_token: torch.Tensor) -> None:
+    blocks().call("hos_keep_last_token", _ptr(step.tokens), _ptr(step.token_seq), _ptr(step.cu_seqlens),
+                  _ptr(step.seq_slot), _ptr(prev_token), int(step.n_seqs), _stream())
+
+
+def scaled_add_norms(a: Optional[torch.Tensor], f: Optional[torch.Tensor], mult: float, x: torch.Tensor,
+                     w1: Optional[torch.Tensor] = None, eps1: float = 0.0, h1: Optional[torch.Tensor] = None,
+                     w2: Optional[torch.Tensor] = None, eps2: float = 0.0, h2: Optional[torch.Tensor] = None) -> None:
+    """x += mult * (a + f) (either may be absent); then h1 = RMSNorm(x; w1, eps1), h2 = RMSNorm(x; w2, eps2)
+    for those that are given."""
+    _check(x, "residual stream", torch.float32, 2)
+    n, d = x.shape
+    for t, what in ((a, "mixer output"), (f, "feed-forward output"), (h1, "first norm output"), (h2, "second norm output")):
+        if t is not None:
+            _check(t, what, None, 2)
+            if t.shape != x.shape:
+                raise KernelError(f"scaled_add_norms: {what} and the residual stream differ in size")
+    if h1 is not None and h2 is not None and h1.dtype != h2.dtype:
+        raise KernelError("scaled_add_norms: the two norm outputs differ in dtype")
+    h = h1 if h1 is not None else h2
+    blocks().call("hos_scaled_add_norms", _ptr(a), dtype_code(a.dtype) if a is not None else 0,
+                  _ptr(f), dtype_code(f.dtype) if f is not None else 0, float(mult), _ptr(x),
+                  _ptr(w1), float(eps1), _ptr(h1), _ptr(w2), float(eps2), _ptr(h2),
+                  dtype_code(h.dtype) if h is not None else 0, n, d, _stream())
+
+
+def latent_prep(proj: torch.Tensor, n_heads: int, dq: int, rank: int, rot: int, w_norm: torch.Tensor, eps: float,
+                inv_freq: Optional[torch.Tensor], rot_dims: int, step, kc: torch.Tensor, q_lat: torch.Tensor,
+                cache: Optional[PagedKVArgs]) -> None:
+    _check(proj, "projection rows", None, 2)
+    _check(kc, "latent rows", proj.dtype, 2)
+    _check(q_lat, "latent queries", torch.float32, 3)
+    n = proj.shape[0]
+    if proj.shape[1] != n_heads * (dq + rot) + rank + rot or kc.shape != (n, rank + rot) \
+            or q_lat.shape != (n, n_heads, rank + rot):
+        raise KernelError("latent_prep: sizes disagree")
+    if cache is not None and (cache.k_pages.dtype != proj.dtype or cache.head_dim != rank + rot or cache.n_kv_heads != 1):
+        raise KernelError("latent_prep: the cache does not fit the latent rows")
+    blocks().call("hos_latent_prep", _ptr(proj), dtype_code(proj.dtype), proj.shape[1], n_heads, dq, rank, rot,
+                  _ptr(w_norm), float(eps), _ptr(inv_freq), int(rot_dims) if inv_freq is not None else 0,
+                  _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(step.seq_len_after),
+                  _ptr(kc), _ptr(q_lat), _ptr(cache.k_pages) if cache else None,
+                  _ptr(cache.page_table) if cache else None, cache.table_stride if cache else 0,
+                  cache.ring_pages if cache else 0, n, _stream())
+
+
+def latent_attn(q_lat: torch.Tensor, kc: Optional[torch.Tensor], cache: Optional[PagedKVArgs], sink: Optional[torch.Tensor],
+                o_lat: torch.Tensor, step, row0: int, rows: int, rank: int, scale: float, window: Optional[int],
+                paged: bool) -> None:
+    """Rows row0 .. row0+rows-1 of the step: keys from `kc` (the step's own rows; sequences from position 0)
+    or from the paged cache."""
+    _check(q_lat, "latent queries", torch.float32, 3)
+    _check(o_lat, "latent outputs", torch.float32, 3)
+    n, heads, d = q_lat.shape
+    if o_lat.shape != (n, heads, rank):
+        raise KernelError("latent_attn: sizes disagree")
+    src = cache.k_pages if paged else kc
+    blocks().call("hos_latent_attn", dtype_code(src.dtype), int(paged), _ptr(q_lat), _ptr(kc),
+                  _ptr(cache.k_pages) if paged else None, _ptr(cache.page_table) if paged else None,
+                  cache.table_stride if paged else 0, cache.ring_pages if paged else 0, _ptr(sink), _ptr(o_lat),
+                  _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot),
+                  int(row0), int(rows), heads, rank, d, float(scale), int(window) if window else 0, _stream())
+
+
+def heads_product(x: torch.Tensor, x_off: int, lda: int, a_head: int, w: torch.Tensor, out: torch.Tensor, out_off: int,
+                  ldo: int, o_head: int, m: int) -> None:
+    """out[r, h, :] = w[h] . x[r, h, :] for all heads in one launch; w: [heads, N, K]; x and out are given with
+    an element offset, a row stride and a head stride (in elements)."""
+    heads, n, k = w.shape
+    blocks().call("hos_heads_product", ctypes.c_void_p(x.data_ptr() + x_off * x.element_size()), dtype_code(x.dtype),
+                  _ptr(w), dtype_code(w.dtype), ctypes.c_void_p(out.data_ptr() + out_off * out.element_size()),
+                  dtype_code(out.dtype), int(m), n, k, heads, int(lda), int(a_head), int(ldo), int(o_head), _stream())
+
+
+def token_shift(h: torch.Tensor, kept: torch.Tensor, mu: torch.Tensor, step, out: torch.Tensor) -> None:
+    _check(h, "rows", None, 2)
+    _check(mu, "mixing weights", torch.float32, 2)
+    _check(out, "shifted rows", h.dtype, 3)
+    n, d = h.shape
+    if out.shape != (mu.shape[0], n, d) or mu.shape[1] != d or kept.shape[1] != d:
+        raise KernelError("token_shift: sizes disagree")
+    blocks().call("hos_token_shift", _ptr(h), dtype_code(h.dtype), _ptr(kept), _ptr(mu), mu.shape[0],
+                  _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out),
+                  n, d, _stream())
+
+
+def tanh_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    _check(x, "rows", torch.float32)
+    _check(out, "tanh output")
+    blocks().call("hos_tanh_rows", _ptr(x), _ptr(out), dtype_code(out.dtype), x.numel(), _stream())
+
+
+def wkv_scan(r, k, v, wx, g, w0, u, norm_w, eps: float, state: torch.Tensor, kept: torch.Tensor, h: torch.Tensor,
+             step, out: torch.Tensor, heads: int, dim: int) -> None:
+    for t in (r, k, v, wx, g):
+        _check(t, "recurrence input", torch.float32, 2)
+        if t.shape != (h.shape[0], heads * dim):
+            raise KernelError("wkv_scan: sizes disagree")
+    _check(state, "recurrent state", torch.float32, 4)
+    _check(out, "recurrence output", h.dtype, 2)
+    blocks().call("hos_wkv_scan", _ptr(r), _ptr(k), _ptr(v), _ptr(wx), _ptr(g), _ptr(w0), _ptr(u), _ptr(norm_w),
+                  float(eps), _ptr(state), _ptr(kept), _ptr(h), dtype_code(h.dtype), h.shape[1], _ptr(step.token_pos),
+                  _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out), int(step.n_seqs),
+                  heads, dim, _stream())
+
+
+_moe_tile: Optional[int] = None
+
+
+def moe_tile_rows() -> int:
+    global _moe_tile
+    if _moe_tile is None:
+        f = blocks().lib.hos_moe_tile_rows
+        f.restype, f.argtypes = ctypes.c_int, []
+        _moe_tile = int(f())
+    return _moe_tile
+
+
+def moe_route(h, router, correction, token_seq, choice, weight, top: int) -> None:
+    _check(h, "rows", None, 2)
+    _check(router, "router", torch.float32, 2)
+    n, d = h.shape
+    blocks().call("hos_moe_route", _ptr(h), dtype_code(h.dtype), _ptr(router), _ptr(correction), _ptr(token_seq),
+                  _ptr(choice), _ptr(weight), n, d, router.shape[0], int(top), _stream())
+
+
+def moe_align(choice, n_experts: int, listed, tile_expert) -> None:
+    blocks().call("hos_moe_align", _ptr(choice), choice.numel(), int(n_experts), _ptr(listed), listed.numel(),
+                  _ptr(tile_expert), tile_expert.numel(), _stream())
+
+
+def moe_gate_up(h, w, listed, tile_expert, y, top: int, limit: float, alpha: float) -> None:
+    _check(w, "expert gate/up weights", h.dtype, 3)
+    blocks().call("hos_moe_gate_up", _ptr(h), _ptr(w), dtype_code(h.dtype), _ptr(listed), _ptr(tile_expert), _ptr(y),
+                  tile_expert.numel(), h.shape[1], w.shape[1] // 2, int(top), float(limit), float(alpha), _stream())
+
+
+def moe_down(y, w, listed, tile_expert, weight, pair_out) -> None:
+    _check(w, "expert down weights", y.dtype, 3)
+    blocks().call("hos_moe_down", _ptr(y), _ptr(w), dtype_code(y.dtype), _ptr(listed), _ptr(tile_expert), _ptr(weight),
+                  _ptr(pair_out), tile_expert.numel(), w.shape[1], w.shape[2], _stream())
+
+
+def moe_combine(pair_out, choice, weight, h, out, top: int, n_experts: int) -> None:
+    n, d = h.shape
+    blocks().call("hos_moe_combine", _ptr(pair_out), _ptr(choice), _ptr(weight), _ptr(h), dtype_code(h.dtype), _ptr(out),
+                  n, d, int(top), int(n_experts), _stream())

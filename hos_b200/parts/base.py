@@ -32,7 +32,7 @@ from ..config.base import PartSpec
 class WeightSpec:
     """A tensor a part wants from the checkpoint."""
     name: str                        # checkpoint name
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]           # -1: a size that only the checkpoint's tensor gives
     role: str                        # "matrix", "vector" or "table"
     init_std: float                  # standard deviation of the random-weights mode
     fallback: Optional[str] = None   # another tensor to use when this one is absent (tied head)
@@ -45,6 +45,8 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: Optional[int]            # None: all keys; an int: the last `window` keys
+    keys_only: bool = False          # True: one array per entry instead of two (a mixer whose values are a part
+                                     # of what it keeps as keys, e.g. a shared latent row per position)
 
 
 @dataclass(frozen=True)
@@ -179,6 +181,11 @@ class Part:
     def weight_specs(self) -> List[WeightSpec]:
         return []
 
+    def state_needs(self) -> List[StateNeed]:
+        """Per-sequence state of fixed size that the part keeps (a mixer's is found in its entry's
+        `CallStore.state`, an embedding's in the store the model hands to its `forward`)."""
+        return []
+
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         """Receive the tensors named in weight_specs(), on the device, in their stored
         dtype (bfloat16 kept, 32-bit kept).  Convert or fuse them here, once."""
@@ -201,9 +208,6 @@ class Part:
 class Mixer(Part):
     def kv_need(self) -> Optional[KVNeed]:
         return None
-
-    def state_needs(self) -> List[StateNeed]:
-        return []
 
     def forward(self, h: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
         raise NotImplementedError

@@ -6,6 +6,9 @@ sums are 32-bit.
     x += post_mixer(mixer(pre_mixer(x)));  x += post_ffn(ffn(pre_ffn(x)))
 "prenorm" (the reference's other families): a norm before each branch only,
     x += mixer(pre_mixer(x));  x += ffn(pre_ffn(x))
+"parallel": both branches read a norm (each its own weight) of the SAME x, and their sum is scaled,
+    x += mult * (mixer(pre_mixer(x)) + ffn(pre_ffn(x)))
+    (`mult`: the arrangement's own constant, LayerSpec.params["residual_mult"], default 1).
 """
 from __future__ import annotations
 
@@ -86,5 +89,43 @@ class PreNormLayer(Layer):
         ops.residual_add(f, x)
 
 
+class ParallelLayer(Layer):
+    """x += mult * (mixer(n1(x)) + ffn(n2(x))), n1 and n2 norms of the same x.  One kernel makes the sum and
+    both norms of the NEXT layer's input (or the model's last norm), so a layer costs one row-wise launch."""
+    norm_roles = ("pre_mixer", "pre_ffn")
+    chains = True
+
+    def __init__(self, spec: LayerSpec, rt: Runtime):
+        super().__init__(spec, rt)
+        from .norm import NormPair, RMSNorm
+        n = self.norms
+        if not all(isinstance(n[r], RMSNorm) for r in self.norm_roles):
+            raise SpecError("arch spec error: the parallel arrangement takes RMS norms")
+        self.mult = float(spec.params.get("residual_mult", 1.0))
+        self._pair = NormPair(n["pre_mixer"], n["pre_ffn"])
+
+    def entry_norm(self):
+        return self._pair
+
+    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore, h_in=None, next_norm=None):
+        from .norm import NormPair, RMSNorm
+        h1, h2 = h_in if h_in is not None else self._pair.forward(x)
+        a = self.mixer.forward(h1, step, store)
+        f = self.feed_forward.forward(h2, step)
+        if isinstance(next_norm, NormPair):
+            o1 = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+            o2 = torch.empty_like(o1)
+            ops.scaled_add_norms(a, f, self.mult, x, next_norm.first.weight, next_norm.first.eps, o1,
+                                 next_norm.second.weight, next_norm.second.eps, o2)
+            return o1, o2
+        if isinstance(next_norm, RMSNorm) and not next_norm.add_one:
+            o1 = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+            ops.scaled_add_norms(a, f, self.mult, x, next_norm.weight, next_norm.eps, o1)
+            return o1
+        ops.scaled_add_norms(a, f, self.mult, x)
+        return next_norm.forward(x) if next_norm is not None else None
+
+
 register_part("arrangement", "sandwich", SandwichLayer)
+register_part("arrangement", "parallel", ParallelLayer)
 register_part("arrangement", "prenorm", PreNormLayer)

@@ -12,7 +12,7 @@ import torch
 from .. import ops
 from ..registry import register_part
 from . import linear
-from .base import Part, StepInfo, WeightSpec
+from .base import CallStore, Part, StateNeed, StepInfo, WeightSpec
 
 
 class ScaledEmbedding(Part):
@@ -34,6 +34,43 @@ class ScaledEmbedding(Part):
     def forward(self, tokens: torch.Tensor, step: StepInfo = None) -> torch.Tensor:
         x = torch.empty((tokens.shape[0], self.width), dtype=torch.float32, device=tokens.device)
         ops.embed(tokens, self.table, self.scale, x)
+        return x
+
+
+class PairHashEmbedding(Part):
+    """x = E[token] + B[row]: a second table indexed by a hash of the token and the one before it,
+    row = (previous * mul_prev + token * mul_cur) mod buckets, and row `buckets` (the table's last) for a
+    sequence's first token.  The sum is 32-bit.  The previous token of a sequence that is under way is
+    per-sequence state (one int per slot), moved on after every step."""
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.vocab, self.width = int(p["vocab"]), int(p["width"])
+        self.buckets, self.mul_prev, self.mul_cur = int(p["buckets"]), int(p["mul_prev"]), int(p["mul_cur"])
+        self.table: Optional[torch.Tensor] = None
+        self.pair_table: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w = self.spec.weights
+        return [WeightSpec(w["table"], (self.vocab, self.width), "table", 0.02),
+                WeightSpec(w["pair_table"], (self.buckets + 1, self.width), "table", 0.02)]
+
+    def state_needs(self) -> List[StateNeed]:
+        return [StateNeed("prev_token", (), torch.int32)]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.table = self._matrix(tensors[self.spec.weights["table"]])
+        self.pair_table = self._matrix(tensors[self.spec.weights["pair_table"]])
+        if self.table.dtype != self.pair_table.dtype:
+            self.table, self.pair_table = self.table.float(), self.pair_table.float()
+
+    def forward(self, tokens: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
+        x = torch.empty((tokens.shape[0], self.width), dtype=torch.float32, device=tokens.device)
+        prev = store.state["prev_token"]
+        ops.embed_pair(step, prev, self.table, self.pair_table, self.buckets, self.mul_prev, self.mul_cur, x)
+        ops.keep_last_token(step, prev)
         return x
 
 
@@ -61,4 +98,5 @@ class LinearHead(Part):
 
 
 register_part("embedding", "scaled_embedding", ScaledEmbedding)
+register_part("embedding", "pair_hash_embedding", PairHashEmbedding)
 register_part("head", "linear_head", LinearHead)

@@ -54,4 +54,13 @@ class GatedMLP(FeedForward):
         return linear.matmul_or_partials(z, self.w_down)
 
 
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: its output is None, which the arrangement leaves out of the sum."""
+    graph_safe = True
+
+    def forward(self, h: torch.Tensor, step: StepInfo = None):
+        return None
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "none", NoFeedForward)

@@ -1,0 +1,86 @@
+"""A routed feed-forward (mixture of experts).
+
+Router logits z = W_router h in 32-bit; scores s = softmax(z) over all router outputs.  The `top`
+outputs with the largest s + correction are chosen (the correction, if the model has one, only
+steers the choice); each chosen expert's output is weighted by its plain score s, not renormalised.
+The last `identity` router outputs are experts without tensors whose output is the row itself.
+Expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1),
+output W_down y; no biases.  The step stays on the device: rows are listed expert by expert and the
+experts' products run as tiles of one launch each (csrc/moe.cu); the output is the 32-bit sum.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping
+
+import torch
+
+from .. import ops
+from ..errors import SpecError
+from ..registry import register_part
+from .base import FeedForward, StepInfo, WeightSpec
+
+
+class RoutedExperts(FeedForward):
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.width, self.inner = int(p["width"]), int(p["inner"])
+        self.n_experts, self.n_identity, self.top = int(p["experts"]), int(p.get("identity", 0)), int(p["top"])
+        self.limit = float(p.get("limit") or 0.0)
+        self.alpha = float(p.get("alpha", 1.702))
+        self.has_correction = bool(p.get("correction", False))
+        if self.n_experts < 0 or self.n_identity < 0 or not 0 < self.top <= self.n_experts + self.n_identity:
+            raise SpecError(f"arch spec error: {self.top} of {self.n_experts} + {self.n_identity} experts cannot be chosen")
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w = self.spec.weights
+        out = [WeightSpec(w["router"], (self.n_experts + self.n_identity, self.width), "matrix", 0.3)]
+        if self.has_correction:
+            out.append(WeightSpec(w["correction"], (self.n_experts + self.n_identity,), "vector", 0.05))
+        for e in range(self.n_experts):
+            base = w["expert"].format(e)
+            out += [WeightSpec(base + w["gate"], (self.inner, self.width), "matrix", 0.05),
+                    WeightSpec(base + w["up"], (self.inner, self.width), "matrix", 0.05),
+                    WeightSpec(base + w["down"], (self.width, self.inner), "matrix", 0.05)]
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        w = self.spec.weights
+        self.router = tensors[w["router"]].to(torch.float32).contiguous()
+        self.correction = self._vector32(tensors[w["correction"]]) if self.has_correction else None
+        dev = self.router.device
+        dt = torch.float32 if self.rt.is_fp32 else torch.bfloat16
+        self.w_gate_up = torch.empty((max(1, self.n_experts), 2 * self.inner, self.width), dtype=dt, device=dev)
+        self.w_down = torch.empty((max(1, self.n_experts), self.width, self.inner), dtype=dt, device=dev)
+        for e in range(self.n_experts):
+            base = w["expert"].format(e)
+            self.w_gate_up[e, : self.inner] = tensors[base + w["gate"]]
+            self.w_gate_up[e, self.inner:] = tensors[base + w["up"]]
+            self.w_down[e] = tensors[base + w["down"]]
+
+    def forward(self, h: torch.Tensor, step: StepInfo = None) -> torch.Tensor:
+        n, dev = h.shape[0], h.device
+        top, tile = self.top, ops.moe_tile_rows()
+        pairs = n * top
+        choice = torch.empty(pairs, dtype=torch.int32, device=dev)
+        weight = torch.empty(pairs, dtype=torch.float32, device=dev)
+        ops.moe_route(h, self.router, self.correction, step.token_seq, choice, weight, top)
+        out = torch.empty((n, self.width), dtype=torch.float32, device=dev)
+        pair_out = None
+        if self.n_experts > 0:
+            # every expert's list is padded to whole tiles: at most this many tiles whatever the router chooses
+            max_tiles = min(pairs, self.n_experts) + pairs // tile
+            listed = torch.empty(max_tiles * tile, dtype=torch.int32, device=dev)
+            tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+            ops.moe_align(choice, self.n_experts, listed, tile_expert)
+            y = torch.empty((max_tiles * tile, self.inner), dtype=h.dtype, device=dev)
+            ops.moe_gate_up(h, self.w_gate_up, listed, tile_expert, y, top, self.limit, self.alpha)
+            pair_out = torch.empty((pairs, self.width), dtype=torch.float32, device=dev)
+            ops.moe_down(y, self.w_down, listed, tile_expert, weight, pair_out)
+        ops.moe_combine(pair_out, choice, weight, h, out, top, self.n_experts)
+        return out
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

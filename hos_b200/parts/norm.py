@@ -50,3 +50,20 @@ class RMSNorm(Norm):
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+
+
+class NormPair:
+    """Two RMSNorms of the same row, from one kernel: what a block needs whose mixer and feed-forward both
+    read a norm of the same residual stream.  `forward(x)` gives (first, second)."""
+
+    def __init__(self, first: RMSNorm, second: RMSNorm):
+        if first.add_one or second.add_one:
+            raise ValueError("a pair of norms takes plain weights")
+        self.first, self.second = first, second
+
+    def forward(self, x: torch.Tensor):
+        h1 = torch.empty(x.shape, dtype=self.first.rt.dtype, device=x.device)
+        h2 = torch.empty_like(h1)
+        ops.scaled_add_norms(None, None, 0.0, x, self.first.weight, self.first.eps, h1,
+                             self.second.weight, self.second.eps, h2)
+        return h1, h2

@@ -56,10 +56,13 @@ def resolve_architecture(raw: Mapping[str, Any]) -> str:
         for a in archs:
             if a in _architectures:
                 return a
+    one = raw.get("architecture")          # some formats name theirs in a single string
+    if isinstance(one, str) and one in _architectures:
+        return one
     mt = raw.get("model_type")
     if isinstance(mt, str) and mt in _model_types:
         return _model_types[mt]
-    named = archs if archs else mt
+    named = archs if archs else (one if one else mt)
     raise UnsupportedArchError(
         f"unsupported architecture: {named!r} - registered: {', '.join(registered_architectures())}")
 

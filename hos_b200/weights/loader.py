@@ -47,7 +47,7 @@ def check_against(specs: Sequence[WeightSpec], source) -> Dict[str, str]:
                 missing.append(s.name)
                 continue
         _, shape = source.info(name)
-        if tuple(shape) != tuple(s.shape):
+        if len(shape) != len(s.shape) or any(w >= 0 and w != g for w, g in zip(s.shape, shape)):    # -1: any size
             wrong_shape.append((name, tuple(s.shape), tuple(shape)))
         resolve[s.name] = name
         used.add(name)

@@ -17,7 +17,7 @@ from typing import Dict, List, Sequence, Tuple
 import torch
 
 from ..config.base import ModelConfig
-from ..errors import MissingTensorError
+from ..errors import MissingMetaError, MissingTensorError
 from ..parts.base import WeightSpec
 from .safetensors import SINGLE_FILE, write_safetensors
 
@@ -32,6 +32,10 @@ class RandomSource:
                  dtype: torch.dtype = torch.bfloat16):
         # a tensor with a fallback (a tied head) is not generated: the fallback is used
         self._specs: Dict[str, WeightSpec] = {s.name: s for s in specs if s.fallback is None}
+        open_sizes = [s.name for s in self._specs.values() if any(d < 0 for d in s.shape)]
+        if open_sizes:
+            raise MissingMetaError("random weights need every size in the configuration; these tensors have a size "
+                                   "that only a checkpoint gives: " + ", ".join(open_sizes))
         self.seed = seed
         self.device = torch.device(device)
         self.dtype = dtype
