@@ -280,6 +280,145 @@ def run_baseline_workload(args) -> int:
     return 0
 
 
+# ---- --design satapel: the Satapel design beside Gemma-2 at equal size --------------------------------
+# Sizes that resemble a real model's layers.  Gemma-2 "at equal size": the same width, layer count and
+# vocabulary, as many query heads of as many numbers (dim + rot_dim), an intermediate size equal to what a
+# Satapel token uses (top x ff), a window of the same length on its windowed layers.
+SATAPEL_SIZES = {
+    "s": dict(width=1024, vocab=32000, blocks=2, heads=8, dim=64, rot=32, vdim=64, rank=256, window=1024,
+              wkv_heads=16, wkv_dim=64, decay_rank=64, experts=8, identity=1, top=2, ff=1024),
+    "m": dict(width=2048, vocab=32000, blocks=2, heads=16, dim=64, rot=64, vdim=128, rank=512, window=1024,
+              wkv_heads=32, wkv_dim=64, decay_rank=64, experts=16, identity=1, top=2, ff=1536),
+    "l": dict(width=4096, vocab=64000, blocks=1, heads=32, dim=128, rot=64, vdim=128, rank=512, window=2048,
+              wkv_heads=64, wkv_dim=64, decay_rank=128, experts=32, identity=2, top=4, ff=1024),
+}
+FP32_TFLOPS = 148 * 128 * 2 * 1.9e9 / 1e12      # the FMA pipes of 148 SMs at 1.9 GHz: the bound of 32-bit arithmetic
+
+
+def satapel_raw(z):
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"]}}
+    att = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"],
+                     "scale": (z["dim"] + z["rot"]) ** -0.5, "mask": {"size": z["window"]},
+                     "rot": {"base": 10000.0, "dims": z["rot"]}}}
+    rec = {"type": "wkv", "mlp": mlp, "mixer": {"heads": z["wkv_heads"], "dim": z["wkv_dim"], "decay_rank": z["decay_rank"]}}
+    return {"architecture": "Satapel", "vocab": z["vocab"], "width": z["width"], "residual_mult": 0.5, "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 10007}},
+            "layers": [rec, att, att, att] * z["blocks"]}
+
+
+def gemma_raw_like(z):
+    hd = z["dim"] + z["rot"]
+    return dict(architectures=["Gemma2ForCausalLM"], model_type="gemma2", num_hidden_layers=4 * z["blocks"],
+                hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=max(1, z["heads"] // 2),
+                head_dim=hd, intermediate_size=z["top"] * z["ff"], vocab_size=z["vocab"], rope_theta=10000.0,
+                sliding_window=z["window"], max_position_embeddings=8192, query_pre_attn_scalar=hd,
+                attn_logit_softcapping=50.0, final_logit_softcapping=30.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
+
+
+def satapel_kernel_work(z, tokens, batch, ctx):
+    """Per launch of each of the design's own kernels: (bytes that must move, 32-bit FLOPs) for a prompt of
+    `tokens` tokens and for a decode step of `batch` sequences at length `ctx` (bfloat16 storage)."""
+    H, D, R, W = z["heads"], z["rank"] + z["rot"], z["rank"], z["window"]
+    pairs = sum(min(p + 1, W) for p in range(tokens))
+    keys = min(ctx, W)
+    wh, wd, C = z["wkv_heads"], z["wkv_dim"], z["wkv_heads"] * z["wkv_dim"]
+    top, ff, width = z["top"], z["ff"], z["width"]
+    real = z["experts"] / float(z["experts"] + z["identity"])           # share of the choices that are real experts
+    touched = min(z["experts"], batch * top)
+    return {
+        "hos_latent_attn": {"prefill": (tokens * D * 2 + tokens * H * (D + R) * 4, 2.0 * pairs * H * (D + R)),
+                            "decode": (batch * keys * D * 2, 2.0 * batch * keys * H * (D + R))},
+        "hos_wkv_scan": {"prefill": (tokens * C * 4 * 5, 6.0 * tokens * wh * wd * wd),
+                         "decode": (batch * wh * wd * wd * 4 * 2, 6.0 * batch * wh * wd * wd)},
+        "hos_moe_gate_up": {"prefill": (z["experts"] * 2 * ff * width * 2, 4.0 * tokens * top * real * ff * width),
+                            "decode": (touched * 2 * ff * width * 2, 4.0 * batch * top * real * ff * width)},
+        "hos_moe_down": {"prefill": (z["experts"] * ff * width * 2, 2.0 * tokens * top * real * ff * width),
+                         "decode": (touched * ff * width * 2, 2.0 * batch * top * real * ff * width)},
+        "hos_heads_product": {"prefill": (0, 2.0 * tokens * H * R * (z["dim"] + z["vdim"]) / 2),
+                              "decode": (H * R * (z["dim"] + z["vdim"]) * 2 / 2, 2.0 * batch * H * R * (z["dim"] + z["vdim"]) / 2)},
+    }
+
+
+def run_design_comparison(args) -> int:
+    """Prompt and decode throughput of Satapel beside Gemma-2 at equal size, and where each of the design's own
+    kernels stands against its roofline (bytes over the measured copy rate, 32-bit FLOPs over the FMA pipes'
+    rate, whichever is larger).  One JSON line per size."""
+    import random
+    import torch
+    from hos_b200 import Engine, ops
+    from hos_b200.registry import config_from_dict
+    pk, pk_src = peaks()
+    rng = random.Random(0)
+    tokens, ctx = args.prefill_tokens, args.ctx if args.ctx != 8192 else 2048
+    for name in args.sizes.split(","):
+        z = SATAPEL_SIZES[name]
+        line = {"design": "satapel", "size": name, "sizes": z, "prompt_tokens": tokens, "decode_ctx": ctx, "peaks": pk_src,
+                "dtype": "bf16", "data": "synthetic (random weights)"}
+        for which, raw in (("satapel", satapel_raw(z)), ("gemma2_equal_size", gemma_raw_like(z))):
+            cfg = config_from_dict(raw)
+            batches = [int(b) for b in args.batches.split(",")]
+            eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_batch=max(batches),
+                                     max_tokens=max(batches) * (ctx + 64) + tokens + 64, max_seq_len=max(ctx, tokens) + 64)
+            r = eng.runner
+            out = {"prefill_ms": measure_prefill(eng, tokens, rng)}
+            out["prefill_tok_s"] = tokens * 1e3 / out["prefill_ms"]
+            for b in batches:
+                slots = r.admit(b)
+                r.cache.extend_all(slots, [ctx - args.steps - args.warmup] * b)
+                ms, launches = r.decode_steps_timed(slots, [[rng.randrange(r.vocab_size)] for _ in range(b)], args.warmup, args.steps)
+                for s in slots:
+                    r.release(s)
+                out[f"decode_b{b}_ms"] = ms
+                out[f"decode_b{b}_tok_s"] = b * 1e3 / ms
+                out[f"decode_b{b}_launches"] = launches
+            # per kernel: one prompt and one decode step launched kernel by kernel, every call between two events
+            r.use_sessions = False
+            b = batches[-1]
+            kern = {}
+            for phase in ("prefill", "decode"):
+                slots = r.admit(1 if phase == "prefill" else b)
+                if phase == "decode":
+                    r.cache.extend_all(slots, [ctx - 2] * b)
+                    r.write_records(slots, pos=[ctx - 2] * b)
+                    feed = [[rng.randrange(r.vocab_size)] for _ in range(b)]
+                else:
+                    feed = [[rng.randrange(r.vocab_size) for _ in range(tokens)]]
+                r.step(slots, feed)                          # warm-up of this shape
+                if phase == "decode":
+                    ops.time_calls(True)
+                    r.step(slots, [[t[0]] for t in feed])
+                else:
+                    for s in slots:
+                        r.release(s)
+                    slots = r.admit(1)
+                    ops.time_calls(True)
+                    r.step(slots, feed)
+                times = ops.call_times()
+                ops.time_calls(False)
+                for s in slots:
+                    r.release(s)
+                work = satapel_kernel_work(z, tokens, b, ctx) if which == "satapel" else {}
+                rows = {}
+                for fn, (n, ms) in sorted(times.items(), key=lambda kv: -kv[1][1]):
+                    row = {"calls": n, "ms": round(ms, 4)}
+                    if fn in work:
+                        by, fl = work[fn][phase]
+                        t_mem, t_fl = by / (pk["hbm_gbs"] * 1e9), fl / (FP32_TFLOPS * 1e12)
+                        row["roofline_us_per_call"] = round(max(t_mem, t_fl) * 1e6, 2)
+                        row["bound"] = "hbm" if t_mem >= t_fl else "fp32"
+                        row["frac"] = round(max(t_mem, t_fl) * 1e3 / (ms / n), 4)
+                    rows[fn] = row
+                kern[phase] = rows
+            out["kernels"] = kern
+            line[which] = out
+            del eng, r
+            torch.cuda.empty_cache()
+        print(json.dumps(line), flush=True)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -302,6 +441,11 @@ def main() -> int:
                          "instead of all at its end (not the driver's line: how a batch of unequal lengths decodes)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the timed prompt (default: the contract's 2,048)")
+    ap.add_argument("--design", default=None, choices=["satapel"],
+                    help="not the driver's line: prompt and decode throughput of this design beside Gemma-2 at equal "
+                         "size, with its kernels against their rooflines (--sizes, --batches, --ctx, --prefill-tokens)")
+    ap.add_argument("--sizes", default="s,m", help="with --design: which of the sizes s, m, l")
+    ap.add_argument("--batches", default="1,8,64", help="with --design: decode batch sizes")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -314,6 +458,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design:
+        return run_design_comparison(args)
     if args.workload == "baseline":
         return run_baseline_workload(args)
 

@@ -22,11 +22,10 @@ template <typename T>
 __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restrict__ kept, const float* __restrict__ mu,
                                    int n_mix, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                                    const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
-                                   T* __restrict__ out, int N, int D) {
+                                   T* __restrict__ out, long long plane, int D) {
     pdl_enter();
     const int n = blockIdx.x;
     const int seq = token_seq[n];
-    const size_t plane = (size_t)N * D;
     if (seq < 0) {
         for (int d = threadIdx.x; d < D; d += blockDim.x)
             for (int s = 0; s < n_mix; ++s) out[s * plane + (size_t)n * D + d] = from_float<T>(0.f);
@@ -117,17 +116,18 @@ __global__ void wkv_scan_kernel(const float* __restrict__ r, const float* __rest
 
 using namespace hos;
 
-// out: [n_mix][N][D] of the activations' type; mu: [n_mix][D]; kept: [slots][D] 32-bit.
+// out: n_mix planes of [N][D] of the activations' type, `plane` elements apart; mu: [n_mix][D]; kept: [slots][D] 32-bit.
 extern "C" int hos_token_shift(const void* h, int dtype, const float* kept, const float* mu, int n_mix,
                                const int* token_pos, const int* token_seq, const int* cu_seqlens,
-                               const int* seq_slot, void* out, int N, int D, cudaStream_t stream) {
+                               const int* seq_slot, void* out, long long plane, int N, int D, cudaStream_t stream) {
     if (N <= 0) return 0;
+    if (plane < (long long)N * D) HOS_REFUSE("token_shift: the planes overlap");
     if (dtype == kBF16)
         launch_pdl(token_shift_kernel<bf16>, dim3(N), dim3(128), 0, stream, (const bf16*)h, kept, mu, n_mix, token_pos,
-                   token_seq, cu_seqlens, seq_slot, (bf16*)out, N, D);
+                   token_seq, cu_seqlens, seq_slot, (bf16*)out, plane, D);
     else if (dtype == kF32)
         launch_pdl(token_shift_kernel<float>, dim3(N), dim3(128), 0, stream, (const float*)h, kept, mu, n_mix, token_pos,
-                   token_seq, cu_seqlens, seq_slot, (float*)out, N, D);
+                   token_seq, cu_seqlens, seq_slot, (float*)out, plane, D);
     else
         HOS_REFUSE("token_shift: unknown dtype %d", dtype);
     return check_launch("token_shift");

@@ -115,7 +115,7 @@ def bench_prompt(vocab: int, length: int = 16, which: int = 0) -> List[int]:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
-    print("[hos] hos_b200: Gemma-2 generation on one B200", file=sys.stderr)
+    print("[hos] hos_b200: generation on one B200", file=sys.stderr)
     args = parse_args(list(sys.argv[1:] if argv is None else argv))
     t0 = time.perf_counter()
     if not args.random and not (args.model or os.environ.get("HOS_MODEL")):
@@ -162,7 +162,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         print(f"perplexity    : {ppl:.4f}")
         return 0
 
-    prompts = args.prompts or [list(eng.config.bos_token_id) or [2]]
+    prompts = args.prompts or [list(getattr(eng.config, "bos_token_id", ())) or [min(2, eng.vocab_size() - 1)]]
     print(f"[hos] prompt -> {sum(len(p) for p in prompts)} tokens", file=sys.stderr)
     kw = dict(max_tokens=args.n_predict, temp=args.temp, top_k=args.top_k, top_p=args.top_p,
               rep_penalty=args.rep_penalty, repeat_last_n=args.repeat_last_n, seed=args.seed)

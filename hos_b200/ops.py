@@ -125,13 +125,40 @@ class Library:
     def call(self, name: str, *args, signature: Optional[str] = None) -> None:
         global launch_count
         launch_count += 1
-        rc = self.fn(name, signature)(*args)
+        if _call_times is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = self.fn(name, signature)(*args)
+            e1.record()
+            _call_times.append((name, e0, e1))
+        else:
+            rc = self.fn(name, signature)(*args)
         if rc != 0:
             msg = self._last_error() if self._last_error else b""
             raise KernelError((msg or b"").decode(errors="replace") or f"{name} failed with code {rc}")
 
 
 _libraries: List["Library"] = []
+_call_times: Optional[list] = None
+
+
+def time_calls(on: bool) -> None:
+    """Measurement aid: while on, every call into a CUDA library is bracketed by two events on the launching
+    stream (not inside a graph capture); `call_times()` adds them up by function."""
+    global _call_times
+    _call_times = [] if on else None
+
+
+def call_times() -> dict:
+    """{function: (calls, milliseconds in all)} of the calls made since time_calls(True); waits for them."""
+    torch.cuda.synchronize()
+    out = {}
+    for name, e0, e1 in _call_times or []:
+        n, ms = out.get(name, (0, 0.0))
+        out[name] = (n + 1, ms + e0.elapsed_time(e1))
+    if _call_times is not None:
+        _call_times.clear()
+    return out
 _launch_ahead = False
 
 _ERROR_WORD_SETTERS = ("hos_gemm_tc_set_error_word", "hos_attn_decode_set_error_word",
@@ -594,16 +621,19 @@ def heads_product(x: torch.Tensor, x_off: int, lda: int, a_head: int, w: torch.T
                   dtype_code(out.dtype), int(m), n, k, heads, int(lda), int(a_head), int(ldo), int(o_head), _stream())
 
 
-def token_shift(h: torch.Tensor, kept: torch.Tensor, mu: torch.Tensor, step, out: torch.Tensor) -> None:
+def token_shift(h: torch.Tensor, kept: torch.Tensor, mu: torch.Tensor, step) -> List[torch.Tensor]:
+    """The mixes h + (previous row - h) * mu[s], one [N, D] tensor per row of mu (each 16-byte aligned)."""
     _check(h, "rows", None, 2)
     _check(mu, "mixing weights", torch.float32, 2)
-    _check(out, "shifted rows", h.dtype, 3)
     n, d = h.shape
-    if out.shape != (mu.shape[0], n, d) or mu.shape[1] != d or kept.shape[1] != d:
+    if mu.shape[1] != d or kept.shape[1] != d:
         raise KernelError("token_shift: sizes disagree")
+    plane = (n * d + 15) // 16 * 16
+    out = torch.empty(mu.shape[0] * plane, dtype=h.dtype, device=h.device)
     blocks().call("hos_token_shift", _ptr(h), dtype_code(h.dtype), _ptr(kept), _ptr(mu), mu.shape[0],
                   _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out),
-                  n, d, _stream())
+                  plane, n, d, _stream())
+    return [out[s * plane: s * plane + n * d].view(n, d) for s in range(mu.shape[0])]
 
 
 def tanh_rows(x: torch.Tensor, out: torch.Tensor) -> None:

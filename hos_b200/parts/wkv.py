@@ -71,8 +71,7 @@ class MatrixStateRecurrence(Mixer):
     def forward(self, h: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
         n = h.shape[0]
         S, kept = store.state["S"], store.state["last_row"]
-        mixes = torch.empty((len(MIXES), n, self.width), dtype=h.dtype, device=h.device)
-        ops.token_shift(h, kept, self.mu, step, mixes)
+        mixes = ops.token_shift(h, kept, self.mu, step)
         r, k, v, g = (linear.matmul(mixes[i], self.w_proj[i], out_dtype=torch.float32) for i in range(4))
         low = linear.matmul(mixes[4], self.w1, out_dtype=torch.float32)
         t = torch.empty(low.shape, dtype=h.dtype, device=h.device)

@@ -1,0 +1,329 @@
+"""Satapel on the GPU against the plain oracle (tests/plain/satapel_plain.py): every mechanism alone,
+whole prompts, decoding through the cache and the recurrent state, prompts in pieces, batches against
+each request alone, reuse of slots and pages, the edges of windows and pages, the first tokens, the
+sink, and generation through the engine and the replay program."""
+import copy
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+from satapel_cases import (CASES, assert_rows, attention, experts, make_folder, model, oracle_view, recurrence,
+                           row_errors, tokens)
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("satapel")
+    return {k: make_folder(base, raw, seed, k) for k, (raw, seed) in CASES.items()}
+
+
+def _runner(folder, dtype, **kw):
+    from hos_b200.engine import Runner
+    kw.setdefault("max_tokens", 4096)
+    kw.setdefault("max_seq_len", 1024)
+    return Runner.from_folder(folder, dtype=dtype, **kw)
+
+
+def _oracle(folder, seqs):
+    from plain import satapel_plain as P
+    cfg, w = oracle_view(folder)
+    return [P.forward_logits(cfg, w, s) for s in seqs]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
+def test_whole_prompts_of_unequal_lengths(folders, case, dtype):
+    vocab = CASES[case][0]["vocab"]
+    seqs = [tokens(i, n, vocab) for i, n in enumerate((1, 2, 37, 150))]      # 150: beyond two pages and every window
+    want = _oracle(folders[case], seqs)
+    r = _runner(folders[case], dtype)
+    slots = r.admit(len(seqs))
+    got = r.step(slots, seqs, [list(range(len(s))) for s in seqs]).cpu()
+    assert_rows(got, torch.cat(want), dtype, f"case {case}")
+    for s in slots:
+        r.release(s)
+    r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
+def test_a_prompt_then_token_by_token(folders, case, dtype):
+    """Two requests decoded side by side through the replayed single-token step, across page borders (64, 128)
+    and every window's edge; the shorter one leaves first."""
+    vocab = CASES[case][0]["vocab"]
+    seqs = [tokens(20, 150, vocab), tokens(21, 90, vocab)]
+    plens = [9, 61]
+    want = _oracle(folders[case], seqs)
+    r = _runner(folders[case], dtype)
+    slots = r.admit(2)
+    got = [[r.step(slots, [s[:n] for s, n in zip(seqs, plens)]).cpu()]]
+    got = [[got[0][0][0:1]], [got[0][0][1:2]]]
+    pos, live = list(plens), [0, 1]
+    while live:
+        out = r.step([slots[i] for i in live], [[seqs[i][pos[i]]] for i in live]).cpu()
+        for j, i in enumerate(live):
+            got[i].append(out[j:j + 1])
+            pos[i] += 1
+        for i in [i for i in live if pos[i] == len(seqs[i])]:
+            r.release(slots[i])
+        live = [i for i in live if pos[i] < len(seqs[i])]
+    for i in range(2):
+        assert_rows(torch.cat(got[i]), want[i][plens[i] - 1:], dtype, f"case {case} request {i}")
+    r.cache.check()
+
+
+@pytest.mark.parametrize("case, dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("C", "float32")])
+def test_a_prompt_in_pieces_of_many_sizes(folders, case, dtype):
+    """Pieces down to two tokens and one, with a ring of pages that is only a little longer than the window, so
+    that long pieces run as several passes."""
+    vocab = CASES[case][0]["vocab"]
+    seq = tokens(30, 230, vocab)
+    want = _oracle(folders[case], [seq])[0]
+    r = _runner(folders[case], dtype, chunk_tokens=20)
+    (slot,) = r.admit(1)
+    at, got = 0, []
+    for k in [2, 3, 64, 1, 65, 7, 2, 40, 1, 1, 30, 14]:
+        piece = seq[at:at + k]
+        got.append(r.step([slot], [piece], [list(range(len(piece)))]).cpu())
+        at += len(piece)
+    assert at == len(seq)
+    assert_rows(torch.cat(got), want, dtype, f"case {case}")
+    r.release(slot)
+    r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_batch_gives_what_each_request_gives_alone(folders, dtype):
+    """Also a step in which one request starts while others go on by one token and by several."""
+    vocab = CASES["A"][0]["vocab"]
+    seqs = [tokens(40 + i, n, vocab) for i, n in enumerate((75, 3, 130))]
+    r = _runner(folders["A"], dtype)
+    alone = []
+    for s in seqs:
+        (slot,) = r.admit(1)
+        alone.append(r.step([slot], [s], [list(range(len(s)))]).cpu())
+        r.release(slot)
+    slots = r.admit(3)
+    both = r.step(slots, seqs, [list(range(len(s))) for s in seqs]).cpu()
+    for s in slots:
+        r.release(s)
+    e = row_errors(both, torch.cat(alone))
+    assert float(e.max()) <= (1e-6 if dtype == "float32" else 4e-2)
+    # a mixed step: request 0 goes on by one token, request 2 by nine, request 1 starts
+    slots = r.admit(2)
+    r.step(slots, [seqs[0][:74], seqs[2][:100]])
+    (late,) = r.admit(1)
+    mixed = r.step([late, slots[1], slots[0]], [seqs[1], seqs[2][100:109], seqs[0][74:75]],
+                   [[0, 1, 2], list(range(9)), [0]]).cpu()
+    ref = torch.cat([alone[1], alone[2][100:109], alone[0][74:75]])
+    e = row_errors(mixed, ref)
+    assert float(e.max()) <= (1e-5 if dtype == "float32" else 4e-2)
+    r.cache.check()
+
+
+def test_slots_and_pages_that_are_freed_are_used_again(folders):
+    vocab = CASES["A"][0]["vocab"]
+    first, second = tokens(50, 140, vocab), tokens(51, 100, vocab)
+    want = _oracle(folders["A"], [second])[0]
+    r = _runner(folders["A"], "float32", max_tokens=256)       # four pages: the second request must reuse them
+    (slot,) = r.admit(1)
+    r.step([slot], [first[:130]])
+    for t in first[130:]:
+        r.step([slot], [[t]])
+    pages = set(r.cache.groups[0]._slot_pages[slot])
+    r.release(slot)
+    for g in r.cache.groups:                                  # what a freed page still holds must never be read
+        for k in g.k:
+            k.fill_(1e4)
+    (again,) = r.admit(1)
+    assert again == slot
+    got = [r.step([again], [second[:70]], [list(range(70))]).cpu()]
+    for t in second[70:]:
+        got.append(r.step([again], [[t]]).cpu())
+    assert set(r.cache.groups[0]._slot_pages[again]) <= pages | set(range(4))
+    assert_rows(torch.cat(got), want, "float32", "second request in a used slot")
+    r.release(again)
+    r.cache.check()
+
+
+@pytest.mark.parametrize("case", ["A", "B", "C"])
+def test_the_edge_of_every_window_in_prompts_and_in_decoding(folders, case):
+    """The oracle with every window one key longer, or one shorter, is far from the oracle itself at the probed
+    places (so a window that is off by one cannot pass), and the library agrees with the oracle, whether the
+    probed token comes in a prompt or alone."""
+    from plain import satapel_plain as P
+    raw = CASES[case][0]
+    cfg, w = oracle_view(folders[case])
+    seq = tokens(60, 160, raw["vocab"])
+    want = P.forward_logits(cfg, w, seq)
+    probes = list(range(0, 12)) + list(range(60, 76)) + list(range(124, 160))
+    for delta in (1, -1):
+        other = copy.deepcopy(cfg)
+        for layer in other["layers"]:
+            if layer["mixer"].get("mask") and layer["mixer"]["mask"]["size"] + delta > 0:
+                layer["mixer"]["mask"]["size"] += delta
+        off = row_errors(P.forward_logits(other, w, seq)[probes], want[probes])
+        assert float(off.median()) > 1e-3, "the test would not see a window that is off by one"
+    r = _runner(folders[case], "float32")
+    (slot,) = r.admit(1)
+    assert_rows(r.step([slot], [seq], [probes]).cpu(), want[probes], "float32", "in a prompt")
+    r.release(slot)
+    (slot,) = r.admit(1)
+    r.step([slot], [seq[:5]])
+    got = [r.step([slot], [[t]]).cpu() for t in seq[5:]]
+    assert_rows(torch.cat(got), want[5:], "float32", "decoded alone")
+    r.release(slot)
+
+
+def test_a_far_key_and_the_sink_show_in_the_logits(tmp_path):
+    """One layer that sees all keys, with soft scores and large sinks: without the ten keys that lie more than 390
+    tokens back, or without the sink in the denominator, the oracle's logits move by a hundred times the tolerance."""
+    from plain import satapel_plain as P
+    raw = model(48, 60, [attention(2, 8, 4, 8, 16, 0.5, window=None, mlp=None)], mult=1.0)
+
+    def edit(t):
+        t["l0.mix.sink"] = torch.tensor([6.0, 2.0])
+    folder = make_folder(tmp_path, raw, 5, "far", edit)
+    cfg, w = oracle_view(folder)
+    seq = tokens(70, 400, 60)
+    want = P.forward_logits(cfg, w, seq)
+    assert float(row_errors(P.forward_logits(cfg, w, seq, use_sink=False), want).median()) > 1e-2
+    short = P.forward_logits(cfg, w, seq, window_override=390)
+    assert float(row_errors(short[395:], want[395:]).median()) > 1e-4
+    for dtype in ("float32", "bfloat16"):
+        r = _runner(folder, dtype)
+        (slot,) = r.admit(1)
+        got = [r.step([slot], [seq[:380]], [list(range(380))]).cpu()] + [r.step([slot], [[t]]).cpu() for t in seq[380:]]
+        assert_rows(torch.cat(got), want, dtype, "a layer that sees all keys")
+        r.release(slot)
+
+
+def test_every_layer_and_the_embedding_alone(folders):
+    """The residual stream after the embedding and after every layer, in 32-bit, for a prompt and for its last
+    tokens one by one; then single-layer models of each mixer without a feed-forward."""
+    from plain import satapel_plain as P
+    for case in ("A", "B"):
+        cfg, w = oracle_view(folders[case])
+        seq = tokens(80, 90, cfg["vocab"])
+        want = P.layer_states(cfg, w, seq)
+        r = _runner(folders[case], "float32")
+        (slot,) = r.admit(1)
+        taps = r.hidden_states([slot], [seq])
+        assert float((taps[0].cpu().double() - want[0]).abs().max()) < 1e-6          # the embedding: a 32-bit sum
+        for i, (g, x) in enumerate(zip(taps, want)):
+            assert float(row_errors(g.cpu(), x).max()) < 1e-5, f"case {case}: after layer {i}"
+        r.release(slot)
+
+
+def test_the_routed_feed_forward_alone(folders):
+    """The part by itself: more rows than one tile for an expert, a single row, rows that are padding."""
+    from plain import satapel_plain as P
+    from hos_b200.parts.base import Runtime, StepInfo
+    from hos_b200.parts.moe import RoutedExperts
+    from hos_b200.registry import config_from_dict, plan_for
+    for case, layer in (("A", 1), ("C", 0)):
+        cfg, w = oracle_view(folders[case])
+        spec = plan_for(config_from_dict(cfg)).layers[layer].feed_forward
+        for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 3e-2)):
+            part = RoutedExperts(spec, Runtime(torch.device("cuda"), dtype))
+            names = [s.name for s in part.weight_specs()]
+            part.bind({n: w[n].to("cuda", torch.bfloat16) for n in names})
+            for n in (1, 7, 300):
+                torch.manual_seed(n)
+                h = torch.randn(n + 2, cfg["width"], dtype=torch.float64).to(torch.bfloat16)
+                seqs = torch.zeros(n + 2, dtype=torch.int32)
+                seqs[n:] = -1                                               # two padding rows
+                step = StepInfo(n + 2, 1, None, None, seqs.cuda(), None, None, None, False, False, n, n)
+                got = part.forward(h.to("cuda", dtype), step).cpu()
+                want, chosen, pick = P.routed_experts(cfg["layers"][layer]["mlp"], w, f"l{layer}.mlp.", h[:n].double())
+                assert float(got[n:].abs().max()) == 0.0
+                e = row_errors(got[:n], want)
+                if dtype == torch.float32:
+                    assert float(e.max()) <= tol
+                else:
+                    assert float((e <= tol).double().mean()) >= 0.9
+
+
+def test_other_constants_of_the_pair_table_and_the_first_tokens(tmp_path):
+    """Multipliers whose products pass 32 bits, one bucket, and a request of one token that is then decoded."""
+    raw = model(40, 3000, [recurrence(2, 8, 4, mlp=None)], buckets=1, mul_prev=2 ** 31 - 1, mul_cur=2 ** 29 + 3)
+    raw2 = model(40, 3000, [recurrence(2, 8, 4, mlp=None)], buckets=2999, mul_prev=2 ** 31 - 1, mul_cur=2 ** 29 + 3)
+    for i, cfg_raw in enumerate((raw, raw2)):
+        folder = make_folder(tmp_path, cfg_raw, 9, f"pair{i}")
+        seq = tokens(90 + i, 12, 3000)
+        want = _oracle(folder, [seq])[0]
+        r = _runner(folder, "float32")
+        (slot,) = r.admit(1)
+        got = [r.step([slot], [seq[:1]]).cpu()] + [r.step([slot], [[t]]).cpu() for t in seq[1:]]
+        assert_rows(torch.cat(got), want, "float32", "token by token from the first")
+        r.release(slot)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(folders, dtype):
+    """The public entry point and its scheduler: more prompts than run side by side, unequal lengths."""
+    from plain import satapel_plain as P
+    from hos_b200 import Engine
+    cfg, w = oracle_view(folders["A"])
+    prompts = [tokens(100 + i, n, cfg["vocab"]) for i, n in enumerate((5, 70, 1))]
+    eng = Engine(folders["A"], dtype=dtype, max_batch=2, max_seq_len=256)
+    got = eng.generate_ids(prompts, 10, stop_ids=[])
+    if dtype == "float32":
+        assert got == [P.greedy(cfg, w, p, 10) for p in prompts]
+    else:
+        for p, g in zip(prompts, got):
+            assert len(g) == 10
+            seq = list(p)
+            for t in g[:4]:
+                l = P.forward_logits(cfg, w, seq)[-1]
+                assert float(l.max() - l[t]) < 0.25, "bfloat16 chose a token far from the best"
+                seq.append(t)
+    eng.runner.cache.check()
+
+
+def test_the_replay_program_on_a_model_folder(folders, tmp_path):
+    vocab = CASES["B"][0]["vocab"]
+    seqs = {"x": tokens(110, 80, vocab), "y": tokens(111, 30, vocab), "z": tokens(112, 1, vocab)}
+    want = dict(zip(seqs, _oracle(folders["B"], list(seqs.values()))))
+    steps, rows = [], {}
+    steps.append({"step": 0, "entries": [{"id": "z", "tokens": seqs["z"], "want": [0]}], "end": ["z"]})
+    rows[0] = [("z", 0)]
+    steps.append({"step": 1, "entries": [{"id": "x", "tokens": seqs["x"][:70], "want": [0, 69]},
+                                         {"id": "y", "tokens": seqs["y"][:25], "want": []}], "end": []})
+    rows[1] = [("x", 0), ("x", 69)]
+    for k in range(10):
+        ents = [{"id": "x", "tokens": [seqs["x"][70 + k]], "want": [0]}]
+        rws = [("x", 70 + k)]
+        if k < 5:
+            ents.append({"id": "y", "tokens": [seqs["y"][25 + k]], "want": [0] if k % 2 else []})
+            if k % 2:
+                rws.append(("y", 25 + k))
+        steps.append({"step": 2 + k, "entries": ents, "end": (["y"] if k == 4 else []) + (["x"] if k == 9 else [])})
+        rows[2 + k] = rws
+    out = str(tmp_path / "out")
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folders["B"], "--dtype", "float32", "--out", out,
+                        "--max-tokens", "256"], input="".join(json.dumps(s) + "\n" for s in steps).encode(),
+                       stdout=subprocess.PIPE, stderr=subprocess.PIPE, timeout=900)
+    assert p.returncode == 0, p.stderr.decode()[-2000:]
+    assert [l for l in p.stdout.decode().splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+    for n, rws in rows.items():
+        got = torch.from_numpy(np.fromfile(os.path.join(out, f"{n}.f32"), dtype="<f4").reshape(len(rws), vocab).copy())
+        assert_rows(got, torch.stack([want[i][pos] for i, pos in rws]), "float32", f"step {n}")
+
+
+def test_generation_through_the_command_line(folders):
+    from plain import satapel_plain as P
+    cfg, w = oracle_view(folders["B"])
+    prompt = tokens(120, 6, cfg["vocab"])
+    want = P.greedy(cfg, w, prompt, 5)
+    p = subprocess.run([os.path.join(ROOT, "bin", "hos"), "-m", folders["B"], "--fp32", "--repeat-penalty", "1.0", "-n", "5",
+                        "-p", ",".join(map(str, prompt))], stdout=subprocess.PIPE, stderr=subprocess.PIPE, timeout=900)
+    assert p.returncode == 0, p.stderr.decode()[-2000:]
+    assert p.stdout.decode().strip() == ",".join(map(str, prompt + want))
