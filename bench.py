@@ -285,11 +285,11 @@ def run_baseline_workload(args) -> int:
 # vocabulary, as many query heads of as many numbers (dim + rot_dim), an intermediate size equal to what a
 # Satapel token uses (top x ff), a window of the same length on its windowed layers.
 SATAPEL_SIZES = {
-    "s": dict(width=1024, vocab=32000, blocks=2, heads=8, dim=64, rot=32, vdim=64, rank=256, window=1024,
+    "s": dict(width=1024, vocab=32000, blocks=2, heads=8, dim=96, rot=32, vdim=64, rank=256, window=1024,
               wkv_heads=16, wkv_dim=64, decay_rank=64, experts=8, identity=1, top=2, ff=1024),
     "m": dict(width=2048, vocab=32000, blocks=2, heads=16, dim=64, rot=64, vdim=128, rank=512, window=1024,
               wkv_heads=32, wkv_dim=64, decay_rank=64, experts=16, identity=1, top=2, ff=1536),
-    "l": dict(width=4096, vocab=64000, blocks=1, heads=32, dim=128, rot=64, vdim=128, rank=512, window=2048,
+    "l": dict(width=4096, vocab=64000, blocks=1, heads=32, dim=64, rot=64, vdim=128, rank=512, window=2048,
               wkv_heads=64, wkv_dim=64, decay_rank=128, experts=32, identity=2, top=4, ff=1024),
 }
 FP32_TFLOPS = 148 * 128 * 2 * 1.9e9 / 1e12      # the FMA pipes of 148 SMs at 1.9 GHz: the bound of 32-bit arithmetic
@@ -405,9 +405,11 @@ def run_design_comparison(args) -> int:
                     row = {"calls": n, "ms": round(ms, 4)}
                     if fn in work:
                         by, fl = work[fn][phase]
-                        t_mem, t_fl = by / (pk["hbm_gbs"] * 1e9), fl / (FP32_TFLOPS * 1e12)
+                        tensor = fn in ("hos_moe_gate_up", "hos_moe_down")        # bfloat16 products: tensor cores
+                        t_mem = by / (pk["hbm_gbs"] * 1e9)
+                        t_fl = fl / ((pk["bf16_tflops"] if tensor else FP32_TFLOPS) * 1e12)
                         row["roofline_us_per_call"] = round(max(t_mem, t_fl) * 1e6, 2)
-                        row["bound"] = "hbm" if t_mem >= t_fl else "fp32"
+                        row["bound"] = "hbm" if t_mem >= t_fl else ("bf16 tensor" if tensor else "fp32")
                         row["frac"] = round(max(t_mem, t_fl) * 1e3 / (ms / n), 4)
                     rows[fn] = row
                 kern[phase] = rows

@@ -102,139 +102,255 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int proj_stride, 
 }
 
 // ---- latent_attn ---------------------------------------------------------------------------
-// One block per (row, group of kHG heads).  Keys come in tiles of kTK positions, each row brought
-// to shared memory as 32-bit numbers.  Scores: warp = head, lane = key.  Weighted sums: a thread
-// owns up to kNC columns of the latent for all heads of the group.
-constexpr int kHG = 8, kTK = 32, kNC = 4, kAttnThreads = 256;
+// One block per (QT consecutive rows, group of kHG heads, share of the keys).  Keys come in tiles of kTK
+// positions, each row brought to shared memory as 32-bit numbers and used by all QT rows and all heads of the
+// block.  Scores: warp = head, lane = key, QT rows at a time.  Weighted sums: a thread owns up to NC columns of
+// the latent for all rows and heads of the block.  Rows of a block that belong to different sequences are walked
+// one sequence after the other.  With more than one share of the keys (single rows: decoding), every share leaves
+// its running maximum, its denominator and its unnormalised sums, and latent_merge puts them together.
+constexpr int kHG = 8, kTK = 32, kAttnThreads = 256;
 
-template <typename T, bool PAGED>
+template <typename T, bool PAGED, int NC, int QT>
 __global__ void __launch_bounds__(kAttnThreads)
 latent_attn_kernel(const float* __restrict__ q_lat, const T* __restrict__ kc, const T* __restrict__ k_pages,
                    const int* __restrict__ page_table, int table_stride, int ring_pages,
-                   const float* __restrict__ sink, float* __restrict__ o_lat, const int* __restrict__ token_pos,
+                   const float* __restrict__ sink, float* __restrict__ o_lat, float* __restrict__ part_acc,
+                   float* __restrict__ part_ml, const int* __restrict__ token_pos,
                    const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
-                   const int* __restrict__ seq_slot, int row0, int H, int R, int D, int Dq, int Dk, float scale,
-                   int window) {
+                   const int* __restrict__ seq_slot, int row0, int row_end, int H, int R, int D, int Dq, int Dk,
+                   float scale, int window) {
     pdl_enter();
     extern __shared__ float smem[];
-    float* qs = smem;                          // [kHG][Dq]
-    float* ks = qs + kHG * Dq;                 // [kTK][Dk]
-    float* ps = ks + kTK * Dk;                 // [kTK][kHG] weights of the tile
-    float* alpha = ps + kTK * kHG;             // [kHG] what the running sums are scaled by
-    float* denom = alpha + kHG;                // [kHG]
+    float* qs = smem;                          // [QT][kHG][Dq]
+    float* ks = qs + QT * kHG * Dq;            // [kTK][Dk]
+    float* ps = ks + kTK * Dk;                 // [QT][kTK][kHG] weights of the tile
+    float* alpha = ps + QT * kTK * kHG;        // [QT][kHG] what the running sums are scaled by
+    float* denom = alpha + QT * kHG;           // [QT][kHG]
     __shared__ int key_row[kTK];               // where each key of the tile lies (-1: none)
-    const int n = row0 + blockIdx.x, h0 = blockIdx.y * kHG;
+    __shared__ int row_seq[QT], row_pos[QT];
+    const int n0 = row0 + blockIdx.x * QT, h0 = blockIdx.y * kHG;
+    const int split = blockIdx.z, n_splits = gridDim.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nh = min(kHG, H - h0);
-    const int seq = token_seq[n];
-    if (seq < 0) {                             // padding: zeros, so that what follows stays finite
-        for (int i = tid; i < nh * R; i += kAttnThreads) o_lat[((size_t)n * H + h0) * R + i] = 0.f;
-        return;
+    if (tid < QT) {
+        const int n = n0 + tid;
+        row_seq[tid] = n < row_end ? token_seq[n] : -1;
+        row_pos[tid] = n < row_end ? token_pos[n] : 0;
     }
-    const int pos = token_pos[n];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    for (int i = tid; i < kHG * Dq; i += kAttnThreads) {
-        const int h = i / Dq, d = i - h * Dq;
-        qs[i] = (h < nh && d < D) ? q_lat[((size_t)n * H + h0 + h) * D + d] : 0.f;
+    for (int i = tid; i < QT * kHG * Dq; i += kAttnThreads) {
+        const int t = i / (kHG * Dq), rem = i - t * kHG * Dq, h = rem / Dq, d = rem - h * Dq;
+        const int n = n0 + t;
+        qs[i] = (n < row_end && h < nh && d < D) ? q_lat[((size_t)n * H + h0 + h) * D + d] : 0.f;
     }
-    const int seq_first = PAGED ? 0 : cu_seqlens[seq];
-    const int* table = PAGED ? page_table + (size_t)seq_slot[seq] * table_stride : nullptr;
-    float m_run = -INFINITY, l_run = 0.f;      // of head `warp` (kept by every lane of the warp)
-    if (warp < nh && sink != nullptr) {
-        m_run = sink[h0 + warp];
-        l_run = 1.f;
-    }
-    float acc[kNC][kHG];
+    __syncthreads();
+    float m_run[QT], l_run[QT];                // of head `warp`, per row (kept by every lane of the warp)
 #pragma unroll
-    for (int c = 0; c < kNC; ++c)
+    for (int t = 0; t < QT; ++t) {
+        m_run[t] = -INFINITY;
+        l_run[t] = 0.f;
+        if (warp < nh && sink != nullptr && split == 0 && row_seq[t] >= 0) {
+            m_run[t] = sink[h0 + warp];
+            l_run[t] = 1.f;
+        }
+    }
+    float acc[NC][QT][kHG];
 #pragma unroll
-        for (int h = 0; h < kHG; ++h) acc[c][h] = 0.f;
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int t = 0; t < QT; ++t)
+#pragma unroll
+            for (int h = 0; h < kHG; ++h) acc[c][t][h] = 0.f;
 
-    for (int p0 = lo; p0 <= pos; p0 += kTK) {
-        __syncthreads();                       // the tile before is used up (and qs is written)
-        if (tid < kTK) {
-            const int p = p0 + tid;
-            int r = -1;
-            if (p <= pos) {
-                if (PAGED) {
-                    const int lp = p / kPageTokens;
-                    r = table[ring_pages > 0 ? lp % ring_pages : lp] * kPageTokens + p % kPageTokens;
+    for (int g0 = 0; g0 < QT;) {               // the rows of one sequence at a time
+        const int seq = row_seq[g0];
+        int g1 = g0 + 1;
+        while (g1 < QT && row_seq[g1] == seq) ++g1;
+        if (seq < 0) {
+            g0 = g1;
+            continue;
+        }
+        const int pos_first = row_pos[g0], pos_last = row_pos[g1 - 1];
+        const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+        const int tiles = (pos_last - lo + kTK) / kTK;
+        const int per = (tiles + n_splits - 1) / n_splits;
+        const int tile_lo = split * per, tile_hi = min(tiles, tile_lo + per);
+        const int seq_first = PAGED ? 0 : cu_seqlens[seq];
+        const int* table = PAGED ? page_table + (size_t)seq_slot[seq] * table_stride : nullptr;
+        for (int tile = tile_lo; tile < tile_hi; ++tile) {
+            const int p0 = lo + tile * kTK;
+            __syncthreads();                   // the tile before is used up
+            if (tid < kTK) {
+                const int p = p0 + tid;
+                int r = -1;
+                if (p <= pos_last) {
+                    if (PAGED) {
+                        const int lp = p / kPageTokens;
+                        r = table[ring_pages > 0 ? lp % ring_pages : lp] * kPageTokens + p % kPageTokens;
+                    } else {
+                        r = seq_first + p;
+                    }
+                }
+                key_row[tid] = r;
+            }
+            __syncthreads();
+            {
+                const T* base = PAGED ? k_pages : kc;
+                if (sizeof(T) == 2 && (D & 7) == 0) {          // 16 bytes (8 numbers) at a time
+                    const int groups = D >> 3;
+                    for (int x = tid; x < kTK * groups; x += kAttnThreads) {
+                        const int j = x / groups, gq = x - j * groups;
+                        const int r = key_row[j];
+                        float* dst = ks + j * Dk + gq * 8;
+                        if (r < 0) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) dst[e] = 0.f;
+                        } else {
+                            const uint4 raw = *reinterpret_cast<const uint4*>(base + (size_t)r * D + gq * 8);
+                            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                dst[2 * e] = __uint_as_float(w[e] << 16);
+                                dst[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+                            }
+                        }
+                    }
+                    for (int x = tid; x < kTK * (Dk - D); x += kAttnThreads) ks[(x / (Dk - D)) * Dk + D + x % (Dk - D)] = 0.f;
                 } else {
-                    r = seq_first + p;
+                    for (int j = warp; j < kTK; j += kAttnThreads / 32) {
+                        const int r = key_row[j];
+                        float* dst = ks + j * Dk;
+                        const T* src = base + (size_t)max(r, 0) * D;
+                        for (int d = lane; d < Dk; d += 32) dst[d] = (r >= 0 && d < D) ? to_float(src[d]) : 0.f;
+                    }
                 }
             }
-            key_row[tid] = r;
-        }
-        __syncthreads();
-        for (int j = warp; j < kTK; j += kAttnThreads / 32) {
-            const int r = key_row[j];
-            float* dst = ks + j * Dk;
-            if (r < 0) {
-                for (int d = lane; d < Dk; d += 32) dst[d] = 0.f;
-            } else {
-                const T* src = (PAGED ? k_pages : kc) + (size_t)r * D;
-                for (int d = lane; d < Dk; d += 32) dst[d] = d < D ? to_float(src[d]) : 0.f;
+            __syncthreads();
+            if (warp < nh) {
+                const float4* kv = reinterpret_cast<const float4*>(ks + lane * Dk);
+                float s[QT];
+#pragma unroll
+                for (int t = 0; t < QT; ++t) s[t] = 0.f;
+                for (int i = 0; i < (Dq >> 2); ++i) {
+                    const float4 b = kv[i];
+#pragma unroll
+                    for (int t = 0; t < QT; ++t) {
+                        const float4 a = reinterpret_cast<const float4*>(qs + (t * kHG + warp) * Dq)[i];
+                        s[t] = fmaf(a.x, b.x, s[t]);
+                        s[t] = fmaf(a.y, b.y, s[t]);
+                        s[t] = fmaf(a.z, b.z, s[t]);
+                        s[t] = fmaf(a.w, b.w, s[t]);
+                    }
+                }
+                const int kp = p0 + lane;
+#pragma unroll
+                for (int t = 0; t < QT; ++t) {
+                    const bool in_group = t >= g0 && t < g1;
+                    const int pt = row_pos[t];
+                    const bool live = in_group && kp <= pt && (window <= 0 || kp > pt - window);
+                    const float sv = live ? s[t] * scale : -INFINITY;
+                    const float m_new = fmaxf(m_run[t], warp_max(sv));
+                    const float p = live ? expf(sv - m_new) : 0.f;
+                    const float a = m_new == -INFINITY ? 1.f : (m_run[t] == -INFINITY ? 0.f : expf(m_run[t] - m_new));
+                    l_run[t] = fmaf(l_run[t], a, warp_sum(p));
+                    m_run[t] = m_new;
+                    ps[(t * kTK + lane) * kHG + warp] = p;
+                    if (lane == 0) alpha[t * kHG + warp] = a;
+                }
+            } else if (warp < kHG) {
+#pragma unroll
+                for (int t = 0; t < QT; ++t) {
+                    ps[(t * kTK + lane) * kHG + warp] = 0.f;
+                    if (lane == 0) alpha[t * kHG + warp] = 1.f;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const int col = tid + c * kAttnThreads;
+                if (col < R) {
+#pragma unroll
+                for (int t = 0; t < QT; ++t)
+#pragma unroll
+                    for (int h = 0; h < kHG; ++h) acc[c][t][h] *= alpha[t * kHG + h];
+#pragma unroll 2
+                for (int j = 0; j < kTK; ++j) {
+                    const float v = ks[j * Dk + col];
+#pragma unroll
+                    for (int t = 0; t < QT; ++t) {
+                        const float4 pa = *reinterpret_cast<const float4*>(ps + (t * kTK + j) * kHG);
+                        const float4 pb = *reinterpret_cast<const float4*>(ps + (t * kTK + j) * kHG + 4);
+                        acc[c][t][0] = fmaf(pa.x, v, acc[c][t][0]);
+                        acc[c][t][1] = fmaf(pa.y, v, acc[c][t][1]);
+                        acc[c][t][2] = fmaf(pa.z, v, acc[c][t][2]);
+                        acc[c][t][3] = fmaf(pa.w, v, acc[c][t][3]);
+                        acc[c][t][4] = fmaf(pb.x, v, acc[c][t][4]);
+                        acc[c][t][5] = fmaf(pb.y, v, acc[c][t][5]);
+                        acc[c][t][6] = fmaf(pb.z, v, acc[c][t][6]);
+                        acc[c][t][7] = fmaf(pb.w, v, acc[c][t][7]);
+                    }
+                }
+                }
             }
         }
-        __syncthreads();
-        if (warp < nh) {
-            const float4* qv = reinterpret_cast<const float4*>(qs + warp * Dq);
-            const float4* kv = reinterpret_cast<const float4*>(ks + lane * Dk);
-            float s = 0.f;
-            for (int i = 0; i < (Dq >> 2); ++i) {
-                const float4 a = qv[i], b = kv[i];
-                s = fmaf(a.x, b.x, s);
-                s = fmaf(a.y, b.y, s);
-                s = fmaf(a.z, b.z, s);
-                s = fmaf(a.w, b.w, s);
-            }
-            const bool live = key_row[lane] >= 0;
-            s = live ? s * scale : -INFINITY;
-            const float m_new = fmaxf(m_run, warp_max(s));        // finite: a tile's first key is live
-            const float p = live ? expf(s - m_new) : 0.f;
-            const float a = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
-            l_run = fmaf(l_run, a, warp_sum(p));
-            m_run = m_new;
-            ps[lane * kHG + warp] = p;
-            if (lane == 0) alpha[warp] = a;
-        } else if (warp < kHG) {
-            ps[lane * kHG + warp] = 0.f;
-            if (lane == 0) alpha[warp] = 0.f;
-        }
-        __syncthreads();
-        float al[kHG];
+        g0 = g1;
+    }
+    __syncthreads();
+    if (warp < kHG && lane == 0) {
 #pragma unroll
-        for (int h = 0; h < kHG; ++h) al[h] = alpha[h];
-#pragma unroll
-        for (int c = 0; c < kNC; ++c) {
-            const int col = tid + c * kAttnThreads;
-            if (col >= R) break;
-#pragma unroll
-            for (int h = 0; h < kHG; ++h) acc[c][h] *= al[h];
-            for (int j = 0; j < kTK; ++j) {
-                const float v = ks[j * Dk + col];
-                const float4 pa = *reinterpret_cast<const float4*>(ps + j * kHG);
-                const float4 pb = *reinterpret_cast<const float4*>(ps + j * kHG + 4);
-                acc[c][0] = fmaf(pa.x, v, acc[c][0]);
-                acc[c][1] = fmaf(pa.y, v, acc[c][1]);
-                acc[c][2] = fmaf(pa.z, v, acc[c][2]);
-                acc[c][3] = fmaf(pa.w, v, acc[c][3]);
-                acc[c][4] = fmaf(pb.x, v, acc[c][4]);
-                acc[c][5] = fmaf(pb.y, v, acc[c][5]);
-                acc[c][6] = fmaf(pb.z, v, acc[c][6]);
-                acc[c][7] = fmaf(pb.w, v, acc[c][7]);
+        for (int t = 0; t < QT; ++t) {
+            denom[t * kHG + warp] = warp < nh ? l_run[t] : 1.f;
+            if (n_splits > 1 && warp < nh && n0 + t < row_end) {
+                float* ml = part_ml + (((size_t)(n0 + t) * H + h0 + warp) * n_splits + split) * 2;
+                ml[0] = m_run[t];
+                ml[1] = l_run[t];
             }
         }
     }
-    if (warp < kHG && lane == 0) denom[warp] = warp < nh ? l_run : 1.f;
     __syncthreads();
 #pragma unroll
-    for (int c = 0; c < kNC; ++c) {
+    for (int c = 0; c < NC; ++c) {
         const int col = tid + c * kAttnThreads;
-        if (col >= R) break;
+        if (col >= R) continue;
 #pragma unroll
-        for (int h = 0; h < kHG; ++h)
-            if (h < nh) o_lat[((size_t)n * H + h0 + h) * R + col] = acc[c][h] / denom[h];
+        for (int t = 0; t < QT; ++t) {
+            const int n = n0 + t;
+            if (n >= row_end) continue;
+#pragma unroll
+            for (int h = 0; h < kHG; ++h) {
+                if (h >= nh) continue;
+                if (n_splits > 1) {
+                    part_acc[(((size_t)n * H + h0 + h) * n_splits + split) * R + col] = acc[c][t][h];
+                } else {
+                    const float d = denom[t * kHG + h];
+                    o_lat[((size_t)n * H + h0 + h) * R + col] = (row_seq[t] >= 0 && d > 0.f) ? acc[c][t][h] / d : 0.f;
+                }
+            }
+        }
+    }
+}
+
+// o_lat[n][h] = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s over the shares s of the keys.
+__global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                    float* __restrict__ o_lat, const int* __restrict__ token_seq, int row0, int H, int R,
+                                    int n_splits) {
+    pdl_enter();
+    const int n = row0 + blockIdx.x, h = blockIdx.y;
+    float* out = o_lat + ((size_t)n * H + h) * R;
+    if (token_seq[n] < 0) {
+        for (int c = threadIdx.x; c < R; c += blockDim.x) out[c] = 0.f;
+        return;
+    }
+    const float* ml = part_ml + ((size_t)n * H + h) * n_splits * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
+    float den = 0.f;
+    for (int s = 0; s < n_splits; ++s) den += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - M) * ml[2 * s + 1];
+    const float* pa = part_acc + ((size_t)n * H + h) * n_splits * R;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_splits; ++s)
+            if (ml[2 * s] != -INFINITY) v = fmaf(expf(ml[2 * s] - M), pa[(size_t)s * R + c], v);
+        out[c] = den > 0.f ? v / den : 0.f;
     }
 }
 
@@ -300,21 +416,50 @@ static int launch_prep(const void* proj, int proj_stride, int H, int dq, int R, 
     return check_launch("latent_prep");
 }
 
-template <typename T, bool PAGED>
-static int launch_attn(const float* q_lat, const void* kc, const void* k_pages, const int* page_table, int table_stride,
-                       int ring_pages, const float* sink, float* o_lat, const int* token_pos, const int* token_seq,
-                       const int* cu_seqlens, const int* seq_slot, int row0, int rows, int H, int R, int D, float scale,
-                       int window, cudaStream_t stream) {
+template <typename T, bool PAGED, int NC, int QT>
+static int launch_attn_as(const float* q_lat, const void* kc, const void* k_pages, const int* page_table, int table_stride,
+                          int ring_pages, const float* sink, float* o_lat, float* part_acc, float* part_ml, int n_splits,
+                          const int* token_pos, const int* token_seq, const int* cu_seqlens, const int* seq_slot, int row0,
+                          int rows, int H, int R, int D, float scale, int window, cudaStream_t stream) {
     const int Dq = (D + 3) / 4 * 4;
     const int Dk = 4 * (((D + 3) / 4) | 1);        // rows of 16-byte groups, an odd number of them: no bank conflicts
-    const size_t smem = (size_t)(kHG * Dq + kTK * Dk + kTK * kHG + 2 * kHG) * sizeof(float);
+    const size_t smem = (size_t)(QT * kHG * Dq + kTK * Dk + QT * kTK * kHG + 2 * QT * kHG) * sizeof(float);
     if (smem > 200 * 1024) HOS_REFUSE("latent_attn: rows of %d numbers do not fit a block's shared memory", D);
-    auto kernel = latent_attn_kernel<T, PAGED>;
+    auto kernel = latent_attn_kernel<T, PAGED, NC, QT>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_pdl(kernel, dim3(rows, (H + kHG - 1) / kHG), dim3(kAttnThreads), smem, stream, q_lat, (const T*)kc,
-               (const T*)k_pages, page_table, table_stride, ring_pages, sink, o_lat, token_pos, token_seq, cu_seqlens,
-               seq_slot, row0, H, R, D, Dq, Dk, scale, window);
-    return check_launch("latent_attn");
+    launch_pdl(kernel, dim3((rows + QT - 1) / QT, (H + kHG - 1) / kHG, n_splits), dim3(kAttnThreads), smem, stream, q_lat,
+               (const T*)kc, (const T*)k_pages, page_table, table_stride, ring_pages, sink, o_lat, part_acc, part_ml,
+               token_pos, token_seq, cu_seqlens, seq_slot, row0, row0 + rows, H, R, D, Dq, Dk, scale, window);
+    int rc = check_launch("latent_attn");
+    if (rc == 0 && n_splits > 1) {
+        launch_pdl(latent_merge_kernel, dim3(rows, H), dim3(128), 0, stream, (const float*)part_acc, (const float*)part_ml,
+                   o_lat, token_seq, row0, H, R, n_splits);
+        rc = check_launch("latent_merge");
+    }
+    return rc;
+}
+
+// Rows per block: four where many rows share keys (prompts), fewer where the sums would not fit the registers;
+// one with shares of the keys (decoding).
+template <typename T, bool PAGED>
+static int launch_attn(const float* q_lat, const void* kc, const void* k_pages, const int* page_table, int table_stride,
+                       int ring_pages, const float* sink, float* o_lat, float* part_acc, float* part_ml, int n_splits,
+                       int rows_per_block, const int* token_pos, const int* token_seq, const int* cu_seqlens,
+                       const int* seq_slot, int row0, int rows, int H, int R, int D, float scale, int window,
+                       cudaStream_t stream) {
+    const int nc = (R + kAttnThreads - 1) / kAttnThreads;
+#define HOS_AS(NC, QT) return launch_attn_as<T, PAGED, NC, QT>(q_lat, kc, k_pages, page_table, table_stride, ring_pages, sink, \
+                                                               o_lat, part_acc, part_ml, n_splits, token_pos, token_seq,     \
+                                                               cu_seqlens, seq_slot, row0, rows, H, R, D, scale, window, stream)
+    if (rows_per_block <= 1 || n_splits > 1) {
+        if (nc == 1) HOS_AS(1, 1);
+        if (nc == 2) HOS_AS(2, 1);
+        HOS_AS(4, 1);
+    }
+    if (nc == 1) HOS_AS(1, 4);
+    if (nc == 2) HOS_AS(2, 2);
+    HOS_AS(4, 1);
+#undef HOS_AS
 }
 
 }  // namespace hos
@@ -338,17 +483,23 @@ extern "C" int hos_latent_prep(const void* proj, int dtype, int proj_stride, int
 }
 
 // Rows row0 .. row0 + rows - 1 of the step.  paged = 0: keys are the step's own rows `kc` (sequences
-// that start at position 0); paged = 1: keys from `k_pages` through the page table.
+// that start at position 0); paged = 1: keys from `k_pages` through the page table.  n_splits > 1: the keys of
+// every row are cut into that many shares (part_acc: [rows of the step][H][n_splits][R], part_ml: [..][n_splits][2]).
+// rows_per_block: 1, or more where neighbouring rows share their keys (prompts).
 extern "C" int hos_latent_attn(int dtype, int paged, const float* q_lat, const void* kc, const void* k_pages,
                                const int* page_table, int table_stride, int ring_pages, const float* sink,
-                               float* o_lat, const int* token_pos, const int* token_seq, const int* cu_seqlens,
+                               float* o_lat, float* part_acc, float* part_ml, int n_splits, int rows_per_block,
+                               const int* token_pos, const int* token_seq, const int* cu_seqlens,
                                const int* seq_slot, int row0, int rows, int H, int R, int D, float scale, int window,
                                cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (R > kNC * kAttnThreads) HOS_REFUSE("latent_attn: a latent of %d numbers is more than %d", R, kNC * kAttnThreads);
+    if (R > 4 * kAttnThreads) HOS_REFUSE("latent_attn: a latent of %d numbers is more than %d", R, 4 * kAttnThreads);
     if (R > D) HOS_REFUSE("latent_attn: the latent (%d) is longer than the row (%d)", R, D);
-#define HOS_GO(T, PG) return launch_attn<T, PG>(q_lat, kc, k_pages, page_table, table_stride, ring_pages, sink, o_lat, \
-                                                 token_pos, token_seq, cu_seqlens, seq_slot, row0, rows, H, R, D, scale, window, stream)
+    if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (part_acc == nullptr || part_ml == nullptr)))
+        HOS_REFUSE("latent_attn: %d shares of the keys need their buffers", n_splits);
+#define HOS_GO(T, PG) return launch_attn<T, PG>(q_lat, kc, k_pages, page_table, table_stride, ring_pages, sink, o_lat, part_acc, \
+                                                 part_ml, n_splits, rows_per_block, token_pos, token_seq, cu_seqlens, seq_slot,   \
+                                                 row0, rows, H, R, D, scale, window, stream)
     if (dtype == kBF16 && paged) HOS_GO(bf16, true);
     if (dtype == kBF16) HOS_GO(bf16, false);
     if (dtype == kF32 && paged) HOS_GO(float, true);

@@ -17,6 +17,7 @@
 // leave at once, so nothing depends on the host knowing the counts.  Products accumulate in 32-bit;
 // a warp whose rows of a tile are all padding skips the arithmetic.
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 namespace hos {
 
@@ -41,6 +42,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     for (int e = warp; e < n_out; e += nwarps) {
         const float* w = router + (size_t)e * D;
         float s = 0.f;
+#pragma unroll 8
         for (int d = lane; d < D; d += 32) s = fmaf(to_float(row[d]), w[d], s);
         s = warp_sum(s);
         if (lane == 0) {
@@ -268,6 +270,174 @@ moe_down_kernel(const T* __restrict__ y, const T* __restrict__ W, const int* __r
     }
 }
 
+// ---- the bfloat16 products on the tensor cores ----------------------------------------------------
+// Tiles of 64 rows x 64 output features, K in steps of 64 through a ring of kStages shared-memory stages
+// filled by 16-byte asynchronous copies; rows of 128 bytes with their 16-byte groups XOR-permuted by the
+// row so that ldmatrix reads without bank conflicts; 8 warps as 4 (rows) x 2 (features), m16n8k16 MMAs with
+// 32-bit accumulators.  A warp whose 16 rows are all padding issues no MMA (a decode step's tiles hold a
+// few rows each: the launch is then bound by the weights it streams).  K and the row strides must be
+// multiples of 8 (16-byte rows); other sizes take the kernels above.
+constexpr int kStages = 3, kBK = 64;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;            // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// element offset of (row, 16-byte group) in a tile of rows of 64 bf16
+__device__ __forceinline__ int swz(int row, int group) { return row * kBK + ((group ^ (row & 7)) << 3); }
+
+// NB: 1 (down: one weight tile) or 2 (gate and up: two weight tiles, the second F rows further on)
+template <int NB>
+struct TcTile {
+    // stage layout: A [64][64], then NB weight tiles [64][64]
+    static constexpr int kStageElems = (1 + NB) * kTile * kBK;
+    static constexpr int kSmemBytes = kStages * kStageElems * 2;
+};
+
+template <int NB, typename RowPtr>
+__device__ __forceinline__ void tc_mainloop(bf16* smem, RowPtr a_row, const bf16* __restrict__ W, int w_rows, int n0,
+                                            size_t second_tile_offset, int K, bool busy, float (&acc)[NB][4][4]) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int warp_m = warp & 3, warp_n = warp >> 2;
+    const int KT = (K + kBK - 1) / kBK;
+    auto load = [&](int kt, int stage) {
+        bf16* A = smem + stage * TcTile<NB>::kStageElems;
+        const int k0 = kt * kBK;
+        for (int x = tid; x < kTile * 8; x += 256) {
+            const int r = x >> 3, g = x & 7, k = k0 + g * 8;
+            const bf16* src = a_row(r);
+            cp_async16(A + swz(r, g), src ? src + k : (const bf16*)W, src != nullptr && k < K);
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            bf16* B = A + (1 + b) * kTile * kBK;
+            const bf16* Wb = W + b * second_tile_offset;
+            for (int x = tid; x < kTile * 8; x += 256) {
+                const int r = x >> 3, g = x & 7, k = k0 + g * 8, n = n0 + r;
+                const bool ok = n < w_rows && k < K;
+                cp_async16(B + swz(r, g), ok ? Wb + (size_t)n * K + k : W, ok);
+            }
+        }
+    };
+    for (int s = 0; s < kStages - 1; ++s) {
+        if (s < KT) load(s, s);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();
+        if (kt + kStages - 1 < KT) load(kt + kStages - 1, (kt + kStages - 1) % kStages);
+        cp_async_commit();
+        if (!busy) continue;
+        const bf16* A = smem + (kt % kStages) * TcTile<NB>::kStageElems;
+#pragma unroll
+        for (int ks = 0; ks < kBK / 16; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4(a, smem_u32(A + swz(warp_m * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4))));
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                const bf16* B = A + (1 + b) * kTile * kBK;
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {          // two pairs of 8-wide feature tiles
+                    uint32_t w[4];
+                    ldmatrix_x4(w, smem_u32(B + swz(warp_n * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8,
+                                                    ks * 2 + ((lane >> 3) & 1))));
+                    mma_bf16(acc[b][np * 2], a, w[0], w[1]);
+                    mma_bf16(acc[b][np * 2 + 1], a, w[2], w[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+__global__ void __launch_bounds__(256)
+moe_gate_up_tc_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, const int* __restrict__ listed,
+                      const int* __restrict__ tile_expert, bf16* __restrict__ y, int D, int F, int top, float limit,
+                      float alpha) {
+    pdl_enter();
+    extern __shared__ __align__(128) unsigned char raw[];
+    bf16* smem = reinterpret_cast<bf16*>(raw);
+    __shared__ int rows[kTile];
+    const int tile = blockIdx.y, e = tile_expert[tile];
+    if (e < 0) return;
+    const int n0 = blockIdx.x * kTile, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x < kTile) {
+        const int id = listed[tile * kTile + threadIdx.x];
+        rows[threadIdx.x] = id >= 0 ? id / top : -1;
+    }
+    __syncthreads();
+    const int warp_m = warp & 3, warp_n = warp >> 2;
+    bool busy = false;
+    for (int i = 0; i < 16; ++i) busy = busy || rows[warp_m * 16 + i] >= 0;
+    float acc[2][4][4] = {};
+    const bf16* We = W + (size_t)e * 2 * F * D;
+    tc_mainloop<2>(smem, [&](int r) { return rows[r] >= 0 ? h + (size_t)rows[r] * D : (const bf16*)nullptr; }, We, F, n0,
+                   (size_t)F * D, D, busy, acc);
+    if (!busy) return;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        const int n = n0 + warp_n * 32 + nt * 8 + (lane & 3) * 2;
+        if (n >= F) continue;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = warp_m * 16 + (lane >> 2) + half * 8;
+            if (rows[r] < 0) continue;
+            float v[2];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float g = acc[0][nt][half * 2 + c], u = acc[1][nt][half * 2 + c];
+                if (limit > 0.f) {
+                    g = fminf(g, limit);
+                    u = fminf(fmaxf(u, -limit), limit);
+                }
+                v[c] = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+            }
+            *reinterpret_cast<uint32_t*>(y + (size_t)(tile * kTile + r) * F + n) = pack_bf16(v[0], v[1]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+moe_down_tc_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, const int* __restrict__ listed,
+                   const int* __restrict__ tile_expert, const float* __restrict__ weight, float* __restrict__ pair_out,
+                   int D, int F) {
+    pdl_enter();
+    extern __shared__ __align__(128) unsigned char raw[];
+    bf16* smem = reinterpret_cast<bf16*>(raw);
+    __shared__ int ids[kTile];
+    const int tile = blockIdx.y, e = tile_expert[tile];
+    if (e < 0) return;
+    const int n0 = blockIdx.x * kTile, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x < kTile) ids[threadIdx.x] = listed[tile * kTile + threadIdx.x];
+    __syncthreads();
+    const int warp_m = warp & 3, warp_n = warp >> 2;
+    bool busy = false;
+    for (int i = 0; i < 16; ++i) busy = busy || ids[warp_m * 16 + i] >= 0;
+    float acc[1][4][4] = {};
+    const bf16* A = y + (size_t)tile * kTile * F;
+    tc_mainloop<1>(smem, [&](int r) { return ids[r] >= 0 ? A + (size_t)r * F : (const bf16*)nullptr; },
+                   W + (size_t)e * D * F, D, n0, 0, F, busy, acc);
+    if (!busy) return;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int id = ids[warp_m * 16 + (lane >> 2) + half * 8];
+        if (id < 0) continue;
+        const float wt = weight[id];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int n = n0 + warp_n * 32 + nt * 8 + (lane & 3) * 2;
+            if (n < D)
+                *reinterpret_cast<float2*>(pair_out + (size_t)id * D + n) =
+                    make_float2(acc[0][nt][half * 2] * wt, acc[0][nt][half * 2 + 1] * wt);
+        }
+    }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ choice,
                                    const float* __restrict__ weight, const T* __restrict__ h, float* __restrict__ out,
@@ -300,10 +470,10 @@ extern "C" int hos_moe_route(const void* h, int dtype, const float* router, cons
     const size_t smem = (size_t)2 * n_out * sizeof(float);
     if (smem > 48 * 1024) HOS_REFUSE("moe_route: %d router outputs are more than a block's shared memory holds", n_out);
     if (dtype == kBF16)
-        launch_pdl(moe_route_kernel<bf16>, dim3(N), dim3(128), smem, stream, (const bf16*)h, router, correction, token_seq,
+        launch_pdl(moe_route_kernel<bf16>, dim3(N), dim3(256), smem, stream, (const bf16*)h, router, correction, token_seq,
                    choice, weight, D, n_out, top);
     else if (dtype == kF32)
-        launch_pdl(moe_route_kernel<float>, dim3(N), dim3(128), smem, stream, (const float*)h, router, correction, token_seq,
+        launch_pdl(moe_route_kernel<float>, dim3(N), dim3(256), smem, stream, (const float*)h, router, correction, token_seq,
                    choice, weight, D, n_out, top);
     else
         HOS_REFUSE("moe_route: unknown dtype %d", dtype);
@@ -326,7 +496,15 @@ extern "C" int hos_moe_gate_up(const void* h, const void* W, int dtype, const in
     if (max_tiles <= 0) return 0;
     dim3 grid((F + kTile - 1) / kTile, max_tiles);
     if (grid.y > 65535) HOS_REFUSE("moe_gate_up: %d tiles are more than one launch takes", max_tiles);
-    if (dtype == kBF16)
+    if (dtype == kBF16 && D % 8 == 0 && F % 8 == 0 && ((uintptr_t)h | (uintptr_t)W | (uintptr_t)y) % 16 == 0) {
+        static bool set = false;
+        if (!set) {
+            cudaFuncSetAttribute(moe_gate_up_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcTile<2>::kSmemBytes);
+            set = true;
+        }
+        launch_pdl(moe_gate_up_tc_kernel, grid, dim3(256), (size_t)TcTile<2>::kSmemBytes, stream, (const bf16*)h,
+                   (const bf16*)W, listed, tile_expert, (bf16*)y, D, F, top, limit, alpha);
+    } else if (dtype == kBF16)
         launch_pdl(moe_gate_up_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, (const bf16*)W, listed, tile_expert,
                    (bf16*)y, D, F, top, limit, alpha);
     else if (dtype == kF32)
@@ -342,7 +520,15 @@ extern "C" int hos_moe_down(const void* y, const void* W, int dtype, const int* 
     if (max_tiles <= 0) return 0;
     dim3 grid((D + kTile - 1) / kTile, max_tiles);
     if (grid.y > 65535) HOS_REFUSE("moe_down: %d tiles are more than one launch takes", max_tiles);
-    if (dtype == kBF16)
+    if (dtype == kBF16 && D % 8 == 0 && F % 8 == 0 && ((uintptr_t)y | (uintptr_t)W | (uintptr_t)pair_out) % 16 == 0) {
+        static bool set = false;
+        if (!set) {
+            cudaFuncSetAttribute(moe_down_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TcTile<1>::kSmemBytes);
+            set = true;
+        }
+        launch_pdl(moe_down_tc_kernel, grid, dim3(256), (size_t)TcTile<1>::kSmemBytes, stream, (const bf16*)y,
+                   (const bf16*)W, listed, tile_expert, weight, pair_out, D, F);
+    } else if (dtype == kBF16)
         launch_pdl(moe_down_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)y, (const bf16*)W, listed, tile_expert,
                    weight, pair_out, D, F);
     else if (dtype == kF32)

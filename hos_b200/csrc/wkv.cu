@@ -112,6 +112,126 @@ __global__ void wkv_scan_kernel(const float* __restrict__ r, const float* __rest
         for (int c = j; c < width; c += blockDim.x) kept[(size_t)slot * width + c] = to_float(h[(size_t)(hi - 1) * width + c]);
 }
 
+// The same walk with the state in registers, for the head sizes that are compiled in (D).  A column of S is cut
+// into kParts runs of rows, one thread each (thread = (part, column)), so that a head keeps kParts * D threads
+// busy; the parts' sums are added when the head norm is taken.  The tokens come in chunks whose r, k, decay, v
+// and gate rows are brought to shared memory together, so that a chunk costs three barriers instead of three per
+// token; the head norm's sums are taken per chunk, a warp per token.
+template <int D> struct ScanShape {
+    static constexpr int kParts = D <= 16 ? 4 : (D <= 32 ? 8 : (D <= 64 ? 4 : 2));
+    static constexpr int kRows = D / kParts;               // rows of S per thread (a multiple of 4)
+    static constexpr int kThreads = (kParts * D + 31) / 32 * 32;
+    static constexpr int kChunk = D <= 64 ? 16 : 8;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(ScanShape<D>::kThreads)
+wkv_scan_reg_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
+                    const float* __restrict__ wx, const float* __restrict__ g, const float* __restrict__ w0,
+                    const float* __restrict__ u, const float* __restrict__ norm_w, float eps,
+                    float* __restrict__ state, float* __restrict__ kept, const T* __restrict__ h, int width,
+                    const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                    const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, T* __restrict__ out, int H) {
+    pdl_enter();
+    constexpr int kParts = ScanShape<D>::kParts, kRows = ScanShape<D>::kRows, kThreads = ScanShape<D>::kThreads,
+                  kChunk = ScanShape<D>::kChunk;
+    static_assert(kRows % 4 == 0 && kRows * kParts == D, "a thread's rows come four at a time");
+    __shared__ __align__(16) float rs[kChunk][D], ks[kChunk][D], ws[kChunk][D], vs[kChunk][D], gs[kChunk][D],
+        os[kParts][kChunk][D], us[D], scale[kChunk];
+    const int seq = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int j = tid % D, part = tid / D, i0 = part * kRows;
+    const int lo = cu_seqlens[seq], hi = cu_seqlens[seq + 1];
+    if (hi <= lo || token_seq[lo] < 0) return;
+    const int slot = seq_slot[seq];
+    const int C = H * D;
+    float* st = state + ((size_t)slot * H + head) * D * D;
+    const bool fresh = token_pos[lo] == 0;
+    const bool mine = part < kParts;
+    float S[kRows];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) S[i] = (mine && !fresh) ? st[(i0 + i) * D + j] : 0.f;
+    if (tid < D) us[tid] = u[head * D + tid];
+    for (int t0 = lo; t0 < hi; t0 += kChunk) {
+        const int nt = min(kChunk, hi - t0);
+        for (int x = tid; x < nt * D; x += kThreads) {
+            const int t = x / D, c = x - t * D;
+            const size_t at = (size_t)(t0 + t) * C + head * D + c;
+            rs[t][c] = r[at];
+            ks[t][c] = k[at];
+            ws[t][c] = expf(-expf(wx[at] + w0[head * D + c]));
+            vs[t][c] = v[at];
+            gs[t][c] = g[at];
+        }
+        __syncthreads();
+        if (mine) {
+            for (int t = 0; t < nt; ++t) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};          // four chains: the sum does not wait for itself
+                const float vt = vs[t][j];
+#pragma unroll
+                for (int i = 0; i < kRows; i += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][i0 + i]);
+                    const float4 r4 = *reinterpret_cast<const float4*>(&rs[t][i0 + i]);
+                    const float4 w4 = *reinterpret_cast<const float4*>(&ws[t][i0 + i]);
+                    const float4 u4 = *reinterpret_cast<const float4*>(&us[i0 + i]);
+                    const float kv0 = k4.x * vt, kv1 = k4.y * vt, kv2 = k4.z * vt, kv3 = k4.w * vt;
+                    acc[0] = fmaf(r4.x, fmaf(u4.x, kv0, S[i]), acc[0]);
+                    acc[1] = fmaf(r4.y, fmaf(u4.y, kv1, S[i + 1]), acc[1]);
+                    acc[2] = fmaf(r4.z, fmaf(u4.z, kv2, S[i + 2]), acc[2]);
+                    acc[3] = fmaf(r4.w, fmaf(u4.w, kv3, S[i + 3]), acc[3]);
+                    S[i] = fmaf(w4.x, S[i], kv0);
+                    S[i + 1] = fmaf(w4.y, S[i + 1], kv1);
+                    S[i + 2] = fmaf(w4.z, S[i + 2], kv2);
+                    S[i + 3] = fmaf(w4.w, S[i + 3], kv3);
+                }
+                os[part][t][j] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+            }
+        }
+        __syncthreads();
+        for (int t = warp; t < nt; t += kThreads / 32) {
+            float ss = 0.f;
+            for (int i = lane; i < D; i += 32) {
+                float o = os[0][t][i];
+#pragma unroll
+                for (int p = 1; p < kParts; ++p) o += os[p][t][i];
+                os[0][t][i] = o;
+                ss = fmaf(o, o, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) scale[t] = rsqrtf(ss / (float)D + eps);
+        }
+        __syncthreads();
+        for (int x = tid; x < nt * D; x += kThreads) {
+            const int t = x / D, c = x - t * D;
+            const float gt = gs[t][c];
+            out[(size_t)(t0 + t) * C + head * D + c] =
+                from_float<T>(os[0][t][c] * scale[t] * norm_w[head * D + c] * (gt / (1.f + expf(-gt))));
+        }
+        __syncthreads();          // the next chunk's rows overwrite what this one has just read
+    }
+    if (mine) {
+#pragma unroll
+        for (int i = 0; i < kRows; ++i) st[(i0 + i) * D + j] = S[i];
+    }
+    if (head == 0)
+        for (int c = tid; c < width; c += kThreads) kept[(size_t)slot * width + c] = to_float(h[(size_t)(hi - 1) * width + c]);
+}
+
+template <typename T>
+static bool launch_scan_reg(int d, dim3 grid, cudaStream_t stream, const float* r, const float* k, const float* v,
+                            const float* wx, const float* g, const float* w0, const float* u, const float* norm_w,
+                            float eps, float* state, float* kept, const void* h, int width, const int* token_pos,
+                            const int* token_seq, const int* cu_seqlens, const int* seq_slot, void* out, int H) {
+#define HOS_SCAN(DD)                                                                                                  \
+    if (d == DD) {                                                                                                    \
+        launch_pdl(wkv_scan_reg_kernel<T, DD>, grid, dim3(ScanShape<DD>::kThreads), 0, stream, r, k, v, wx, g, w0, u,     \
+                   norm_w, eps, state, kept, (const T*)h, width, token_pos, token_seq, cu_seqlens, seq_slot, (T*)out, H); \
+        return true;                                                                                                  \
+    }
+    HOS_SCAN(16) HOS_SCAN(32) HOS_SCAN(48) HOS_SCAN(64) HOS_SCAN(96) HOS_SCAN(128)
+#undef HOS_SCAN
+    return false;
+}
+
 }  // namespace hos
 
 using namespace hos;
@@ -152,6 +272,12 @@ extern "C" int hos_wkv_scan(const float* r, const float* k, const float* v, cons
     const size_t smem = (size_t)(d * d + 4 * d) * sizeof(float);
     if (d > 1024 || smem > 200 * 1024) HOS_REFUSE("wkv_scan: a head of %d does not fit a block's shared memory", d);
     const int threads = (d + 31) / 32 * 32;
+    if (dtype == kBF16 && launch_scan_reg<bf16>(d, dim3(n_seqs, H), stream, r, k, v, wx, g, w0, u, norm_w, eps, state, kept, h,
+                                                width, token_pos, token_seq, cu_seqlens, seq_slot, out, H))
+        return check_launch("wkv_scan");
+    if (dtype == kF32 && launch_scan_reg<float>(d, dim3(n_seqs, H), stream, r, k, v, wx, g, w0, u, norm_w, eps, state, kept, h,
+                                                width, token_pos, token_seq, cu_seqlens, seq_slot, out, H))
+        return check_launch("wkv_scan");
     if (dtype == kBF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(wkv_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_pdl(wkv_scan_kernel<bf16>, dim3(n_seqs, H), dim3(threads), smem, stream, r, k, v, wx, g, w0, u, norm_w, eps,

@@ -595,18 +595,24 @@ def latent_prep(proj: torch.Tensor, n_heads: int, dq: int, rank: int, rot: int, 
 
 def latent_attn(q_lat: torch.Tensor, kc: Optional[torch.Tensor], cache: Optional[PagedKVArgs], sink: Optional[torch.Tensor],
                 o_lat: torch.Tensor, step, row0: int, rows: int, rank: int, scale: float, window: Optional[int],
-                paged: bool) -> None:
+                paged: bool, n_splits: int = 1, rows_per_block: int = 1) -> None:
     """Rows row0 .. row0+rows-1 of the step: keys from `kc` (the step's own rows; sequences from position 0)
-    or from the paged cache."""
+    or from the paged cache.  `n_splits` > 1: every row's keys are cut into that many shares that run side by side
+    and are merged (few rows: decoding); `rows_per_block` > 1: neighbouring rows share the keys they read (prompts)."""
     _check(q_lat, "latent queries", torch.float32, 3)
     _check(o_lat, "latent outputs", torch.float32, 3)
     n, heads, d = q_lat.shape
     if o_lat.shape != (n, heads, rank):
         raise KernelError("latent_attn: sizes disagree")
     src = cache.k_pages if paged else kc
+    part_acc = part_ml = None
+    if n_splits > 1:
+        part_acc = torch.empty((n, heads, n_splits, rank), dtype=torch.float32, device=q_lat.device)
+        part_ml = torch.empty((n, heads, n_splits, 2), dtype=torch.float32, device=q_lat.device)
     blocks().call("hos_latent_attn", dtype_code(src.dtype), int(paged), _ptr(q_lat), _ptr(kc),
                   _ptr(cache.k_pages) if paged else None, _ptr(cache.page_table) if paged else None,
                   cache.table_stride if paged else 0, cache.ring_pages if paged else 0, _ptr(sink), _ptr(o_lat),
+                  _ptr(part_acc), _ptr(part_ml), int(n_splits), int(rows_per_block),
                   _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot),
                   int(row0), int(rows), heads, rank, d, float(scale), int(window) if window else 0, _stream())
 

@@ -80,6 +80,19 @@ class LatentAttention(Mixer):
     def kv_need(self) -> KVNeed:
         return KVNeed(1, self.row, self.window, keys_only=True)
 
+    def plan(self, rows: int, step: StepInfo):
+        """(shares of the keys, rows per block) for `rows` rows of a step.  Rows of one sequence that follow one another
+        share the keys they read: four to a block (prompts, long pieces).  Few rows, or rows of different sequences
+        (decoding), run one to a block, and their keys are cut into shares so that the GPU is filled about twice: at
+        least two tiles of 32 keys per share, at most 32 shares."""
+        if not step.single_token and rows >= 64:
+            return 1, 4
+        blocks = rows * ((self.n_heads + 7) // 8)
+        sms = ops.sm_count()
+        longest = step.max_len_after
+        keys = min(int(self.window), longest) if self.window else longest
+        return max(1, min(32, (keys + 63) // 64, (2 * sms + blocks - 1) // blocks)), 1
+
     def forward(self, h: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
         n = h.shape[0]
         cache = store.kv
@@ -98,7 +111,9 @@ class LatentAttention(Mixer):
         o_lat = torch.empty((n, H, R), dtype=torch.float32, device=h.device)
         nf = n if step.from_zero else step.fresh_tokens
         if nf > 0:
-            ops.latent_attn(q_lat, kc, None, self.sink, o_lat, step, 0, nf, R, self.scale, self.window, paged=False)
+            shares, per_block = self.plan(nf, step)
+            ops.latent_attn(q_lat, kc, None, self.sink, o_lat, step, 0, nf, R, self.scale, self.window, paged=False,
+                            n_splits=shares, rows_per_block=per_block)
         if nf < n:
             if cache.ring_pages > 0 and not step.replayed:
                 room = cache.ring_pages * ops.PAGE_TOKENS - int(self.window) + 1
@@ -107,7 +122,10 @@ class LatentAttention(Mixer):
                     raise KernelError(f"a step that continues sequences brings {max(news)} tokens to a layer that keeps "
                                       f"a window of {self.window} keys in a ring of {cache.ring_pages * ops.PAGE_TOKENS}: "
                                       f"at most {room} fit")
-            ops.latent_attn(q_lat, None, cache, self.sink, o_lat, step, nf, n - nf, R, self.scale, self.window, paged=True)
+            rows = n - nf
+            shares, per_block = self.plan(rows, step)
+            ops.latent_attn(q_lat, None, cache, self.sink, o_lat, step, nf, rows, R, self.scale, self.window, paged=True,
+                            n_splits=shares, rows_per_block=per_block)
         att = torch.empty((n, H * self.vdim), dtype=h.dtype, device=h.device)
         ops.heads_product(o_lat, 0, H * R, R, self.w_uv, att, 0, H * self.vdim, self.vdim, n)
         return linear.matmul(att, self.w_o)
