@@ -18,6 +18,7 @@
 // products W_uk_h^T q_h and W_uv_h o_h as one launch over all heads).
 #include "common.cuh"
 #include "kv_layout.cuh"
+#include "mma_tile.cuh"
 
 namespace hos {
 
@@ -114,7 +115,7 @@ template <typename T, bool PAGED, int NC, int QT>
 __global__ void __launch_bounds__(kAttnThreads)
 latent_attn_kernel(const float* __restrict__ q_lat, const T* __restrict__ kc, const T* __restrict__ k_pages,
                    const int* __restrict__ page_table, int table_stride, int ring_pages,
-                   const float* __restrict__ sink, float* __restrict__ o_lat, float* __restrict__ part_acc,
+                   const float* __restrict__ sink, T* __restrict__ o_lat, float* __restrict__ part_acc,
                    float* __restrict__ part_ml, const int* __restrict__ token_pos,
                    const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
                    const int* __restrict__ seq_slot, int row0, int row_end, int H, int R, int D, int Dq, int Dk,
@@ -322,7 +323,7 @@ latent_attn_kernel(const float* __restrict__ q_lat, const T* __restrict__ kc, co
                     part_acc[(((size_t)n * H + h0 + h) * n_splits + split) * R + col] = acc[c][t][h];
                 } else {
                     const float d = denom[t * kHG + h];
-                    o_lat[((size_t)n * H + h0 + h) * R + col] = (row_seq[t] >= 0 && d > 0.f) ? acc[c][t][h] / d : 0.f;
+                    o_lat[((size_t)n * H + h0 + h) * R + col] = from_float<T>((row_seq[t] >= 0 && d > 0.f) ? acc[c][t][h] / d : 0.f);
                 }
             }
         }
@@ -330,14 +331,15 @@ latent_attn_kernel(const float* __restrict__ q_lat, const T* __restrict__ kc, co
 }
 
 // o_lat[n][h] = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s over the shares s of the keys.
+template <typename T>
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                    float* __restrict__ o_lat, const int* __restrict__ token_seq, int row0, int H, int R,
+                                    T* __restrict__ o_lat, const int* __restrict__ token_seq, int row0, int H, int R,
                                     int n_splits) {
     pdl_enter();
     const int n = row0 + blockIdx.x, h = blockIdx.y;
-    float* out = o_lat + ((size_t)n * H + h) * R;
+    T* out = o_lat + ((size_t)n * H + h) * R;
     if (token_seq[n] < 0) {
-        for (int c = threadIdx.x; c < R; c += blockDim.x) out[c] = 0.f;
+        for (int c = threadIdx.x; c < R; c += blockDim.x) out[c] = from_float<T>(0.f);
         return;
     }
     const float* ml = part_ml + ((size_t)n * H + h) * n_splits * 2;
@@ -350,7 +352,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const fl
         float v = 0.f;
         for (int s = 0; s < n_splits; ++s)
             if (ml[2 * s] != -INFINITY) v = fmaf(expf(ml[2 * s] - M), pa[(size_t)s * R + c], v);
-        out[c] = den > 0.f ? v / den : 0.f;
+        out[c] = from_float<T>(den > 0.f ? v / den : 0.f);
     }
 }
 
@@ -405,6 +407,37 @@ heads_product_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __r
     }
 }
 
+// The same product for bfloat16 operands on the tensor cores (rows and heads 16-byte aligned, K a multiple of 8).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+heads_product_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, TO* __restrict__ out, int M, int N, int K,
+                        int lda, int a_head, int ldo, int o_head) {
+    pdl_enter();
+    extern __shared__ __align__(128) unsigned char raw[];
+    bf16* smem = reinterpret_cast<bf16*>(raw);
+    const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile, h = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warp_m = warp & 3, warp_n = warp >> 2;
+    const bf16* Ah = A + (size_t)h * a_head;
+    const bool busy = m0 + warp_m * 16 < M;
+    float acc[1][4][4] = {};
+    tc_mainloop<1>(smem, [&](int r) { return m0 + r < M ? Ah + (size_t)(m0 + r) * lda : (const bf16*)nullptr; },
+                   W + (size_t)h * N * K, N, n0, 0, K, busy, acc);
+    if (!busy) return;
+    TO* Oh = out + (size_t)h * o_head;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int m = m0 + warp_m * 16 + (lane >> 2) + half * 8;
+        if (m >= M) continue;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int n = n0 + warp_n * 32 + nt * 8 + (lane & 3) * 2;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+                if (n + c < N) Oh[(size_t)m * ldo + n + c] = from_float<TO>(acc[0][nt][half * 2 + c]);
+        }
+    }
+}
+
 template <typename T>
 static int launch_prep(const void* proj, int proj_stride, int H, int dq, int R, int P, const float* w_norm, float eps,
                        const float* inv_freq, int rot_dims, const int* token_pos, const int* token_seq,
@@ -418,7 +451,7 @@ static int launch_prep(const void* proj, int proj_stride, int H, int dq, int R, 
 
 template <typename T, bool PAGED, int NC, int QT>
 static int launch_attn_as(const float* q_lat, const void* kc, const void* k_pages, const int* page_table, int table_stride,
-                          int ring_pages, const float* sink, float* o_lat, float* part_acc, float* part_ml, int n_splits,
+                          int ring_pages, const float* sink, void* o_lat, float* part_acc, float* part_ml, int n_splits,
                           const int* token_pos, const int* token_seq, const int* cu_seqlens, const int* seq_slot, int row0,
                           int rows, int H, int R, int D, float scale, int window, cudaStream_t stream) {
     const int Dq = (D + 3) / 4 * 4;
@@ -428,12 +461,12 @@ static int launch_attn_as(const float* q_lat, const void* kc, const void* k_page
     auto kernel = latent_attn_kernel<T, PAGED, NC, QT>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(kernel, dim3((rows + QT - 1) / QT, (H + kHG - 1) / kHG, n_splits), dim3(kAttnThreads), smem, stream, q_lat,
-               (const T*)kc, (const T*)k_pages, page_table, table_stride, ring_pages, sink, o_lat, part_acc, part_ml,
+               (const T*)kc, (const T*)k_pages, page_table, table_stride, ring_pages, sink, (T*)o_lat, part_acc, part_ml,
                token_pos, token_seq, cu_seqlens, seq_slot, row0, row0 + rows, H, R, D, Dq, Dk, scale, window);
     int rc = check_launch("latent_attn");
     if (rc == 0 && n_splits > 1) {
-        launch_pdl(latent_merge_kernel, dim3(rows, H), dim3(128), 0, stream, (const float*)part_acc, (const float*)part_ml,
-                   o_lat, token_seq, row0, H, R, n_splits);
+        launch_pdl(latent_merge_kernel<T>, dim3(rows, H), dim3(128), 0, stream, (const float*)part_acc, (const float*)part_ml,
+                   (T*)o_lat, token_seq, row0, H, R, n_splits);
         rc = check_launch("latent_merge");
     }
     return rc;
@@ -443,7 +476,7 @@ static int launch_attn_as(const float* q_lat, const void* kc, const void* k_page
 // one with shares of the keys (decoding).
 template <typename T, bool PAGED>
 static int launch_attn(const float* q_lat, const void* kc, const void* k_pages, const int* page_table, int table_stride,
-                       int ring_pages, const float* sink, float* o_lat, float* part_acc, float* part_ml, int n_splits,
+                       int ring_pages, const float* sink, void* o_lat, float* part_acc, float* part_ml, int n_splits,
                        int rows_per_block, const int* token_pos, const int* token_seq, const int* cu_seqlens,
                        const int* seq_slot, int row0, int rows, int H, int R, int D, float scale, int window,
                        cudaStream_t stream) {
@@ -488,7 +521,7 @@ extern "C" int hos_latent_prep(const void* proj, int dtype, int proj_stride, int
 // rows_per_block: 1, or more where neighbouring rows share their keys (prompts).
 extern "C" int hos_latent_attn(int dtype, int paged, const float* q_lat, const void* kc, const void* k_pages,
                                const int* page_table, int table_stride, int ring_pages, const float* sink,
-                               float* o_lat, float* part_acc, float* part_ml, int n_splits, int rows_per_block,
+                               void* o_lat, float* part_acc, float* part_ml, int n_splits, int rows_per_block,
                                const int* token_pos, const int* token_seq, const int* cu_seqlens,
                                const int* seq_slot, int row0, int rows, int H, int R, int D, float scale, int window,
                                cudaStream_t stream) {
@@ -516,6 +549,22 @@ extern "C" int hos_heads_product(const void* in, int in_dtype, const void* W, in
     if (K <= 0) HOS_REFUSE("heads_product: K must be positive");
     dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
     if (grid.y > 65535 || grid.z > 65535) HOS_REFUSE("heads_product: too many rows or heads for one launch");
+    if (in_dtype == kBF16 && w_dtype == kBF16 && K % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 &&
+        ((uintptr_t)in | (uintptr_t)W) % 16 == 0) {
+        static bool set = false;
+        if (!set) {
+            cudaFuncSetAttribute(heads_product_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcTile<1>::kSmemBytes);
+            cudaFuncSetAttribute(heads_product_tc_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcTile<1>::kSmemBytes);
+            set = true;
+        }
+        if (out_dtype == kF32)
+            launch_pdl(heads_product_tc_kernel<float>, grid, dim3(256), (size_t)TcTile<1>::kSmemBytes, stream, (const bf16*)in,
+                       (const bf16*)W, (float*)out, M, N, K, lda, a_head, ldo, o_head);
+        else
+            launch_pdl(heads_product_tc_kernel<bf16>, grid, dim3(256), (size_t)TcTile<1>::kSmemBytes, stream, (const bf16*)in,
+                       (const bf16*)W, (bf16*)out, M, N, K, lda, a_head, ldo, o_head);
+        return check_launch("heads_product");
+    }
 #define HOS_CASE(da, dw, dout, TA, TW, TO)                                                            \
     if (in_dtype == da && w_dtype == dw && out_dtype == dout) {                                       \
         launch_pdl(heads_product_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, (const TA*)in,       \

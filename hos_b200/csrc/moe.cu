@@ -17,18 +17,16 @@
 // leave at once, so nothing depends on the host knowing the counts.  Products accumulate in 32-bit;
 // a warp whose rows of a tile are all padding skips the arithmetic.
 #include "common.cuh"
-#include "mma_utils.cuh"
+#include "mma_tile.cuh"
 
 namespace hos {
-
-constexpr int kTile = 64;
 
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router,
                                  const float* __restrict__ correction, const int* __restrict__ token_seq,
                                  int* __restrict__ choice, float* __restrict__ weight, int D, int n_out, int top) {
     pdl_enter();
-    extern __shared__ float z[];               // [n_out] scores, then [n_out] taken flags
+    extern __shared__ float z[];               // [n_out] scores, [n_out] taken flags, [warps][n_out] partial sums
     float* taken = z + n_out;
     const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     if (token_seq[n] < 0) {
@@ -38,17 +36,31 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         }
         return;
     }
+    // every thread takes a slice of the row for all router outputs (all loads in flight at once), then the
+    // slices are added: per warp by shuffles, across warps through shared memory
     const T* row = h + (size_t)n * D;
-    for (int e = warp; e < n_out; e += nwarps) {
-        const float* w = router + (size_t)e * D;
-        float s = 0.f;
-#pragma unroll 8
-        for (int d = lane; d < D; d += 32) s = fmaf(to_float(row[d]), w[d], s);
-        s = warp_sum(s);
-        if (lane == 0) {
-            z[e] = s;
-            taken[e] = 0.f;
+    float* part = taken + n_out;               // [nwarps][n_out]
+    for (int e0 = 0; e0 < n_out; e0 += 8) {
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const int ne = min(8, n_out - e0);
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            const float x = to_float(row[d]);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (q < ne) s[q] = fmaf(x, router[(size_t)(e0 + q) * D + d], s[q]);
         }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float v = warp_sum(s[q]);
+            if (lane == 0 && q < ne) part[warp * n_out + e0 + q] = v;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_out; e += blockDim.x) {
+        float v = 0.f;
+        for (int w = 0; w < nwarps; ++w) v += part[w * n_out + e];
+        z[e] = v;
+        taken[e] = 0.f;
     }
     __syncthreads();
     if (warp != 0) return;
@@ -277,84 +289,6 @@ moe_down_kernel(const T* __restrict__ y, const T* __restrict__ W, const int* __r
 // 32-bit accumulators.  A warp whose 16 rows are all padding issues no MMA (a decode step's tiles hold a
 // few rows each: the launch is then bound by the weights it streams).  K and the row strides must be
 // multiples of 8 (16-byte rows); other sizes take the kernels above.
-constexpr int kStages = 3, kBK = 64;
-
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-    const int bytes = valid ? 16 : 0;            // 0: the 16 bytes are filled with zeros
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// element offset of (row, 16-byte group) in a tile of rows of 64 bf16
-__device__ __forceinline__ int swz(int row, int group) { return row * kBK + ((group ^ (row & 7)) << 3); }
-
-// NB: 1 (down: one weight tile) or 2 (gate and up: two weight tiles, the second F rows further on)
-template <int NB>
-struct TcTile {
-    // stage layout: A [64][64], then NB weight tiles [64][64]
-    static constexpr int kStageElems = (1 + NB) * kTile * kBK;
-    static constexpr int kSmemBytes = kStages * kStageElems * 2;
-};
-
-template <int NB, typename RowPtr>
-__device__ __forceinline__ void tc_mainloop(bf16* smem, RowPtr a_row, const bf16* __restrict__ W, int w_rows, int n0,
-                                            size_t second_tile_offset, int K, bool busy, float (&acc)[NB][4][4]) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int warp_m = warp & 3, warp_n = warp >> 2;
-    const int KT = (K + kBK - 1) / kBK;
-    auto load = [&](int kt, int stage) {
-        bf16* A = smem + stage * TcTile<NB>::kStageElems;
-        const int k0 = kt * kBK;
-        for (int x = tid; x < kTile * 8; x += 256) {
-            const int r = x >> 3, g = x & 7, k = k0 + g * 8;
-            const bf16* src = a_row(r);
-            cp_async16(A + swz(r, g), src ? src + k : (const bf16*)W, src != nullptr && k < K);
-        }
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-            bf16* B = A + (1 + b) * kTile * kBK;
-            const bf16* Wb = W + b * second_tile_offset;
-            for (int x = tid; x < kTile * 8; x += 256) {
-                const int r = x >> 3, g = x & 7, k = k0 + g * 8, n = n0 + r;
-                const bool ok = n < w_rows && k < K;
-                cp_async16(B + swz(r, g), ok ? Wb + (size_t)n * K + k : W, ok);
-            }
-        }
-    };
-    for (int s = 0; s < kStages - 1; ++s) {
-        if (s < KT) load(s, s);
-        cp_async_commit();
-    }
-    for (int kt = 0; kt < KT; ++kt) {
-        cp_async_wait<kStages - 2>();
-        __syncthreads();
-        if (kt + kStages - 1 < KT) load(kt + kStages - 1, (kt + kStages - 1) % kStages);
-        cp_async_commit();
-        if (!busy) continue;
-        const bf16* A = smem + (kt % kStages) * TcTile<NB>::kStageElems;
-#pragma unroll
-        for (int ks = 0; ks < kBK / 16; ++ks) {
-            uint32_t a[4];
-            ldmatrix_x4(a, smem_u32(A + swz(warp_m * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4))));
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                const bf16* B = A + (1 + b) * kTile * kBK;
-#pragma unroll
-                for (int np = 0; np < 2; ++np) {          // two pairs of 8-wide feature tiles
-                    uint32_t w[4];
-                    ldmatrix_x4(w, smem_u32(B + swz(warp_n * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8,
-                                                    ks * 2 + ((lane >> 3) & 1))));
-                    mma_bf16(acc[b][np * 2], a, w[0], w[1]);
-                    mma_bf16(acc[b][np * 2 + 1], a, w[2], w[3]);
-                }
-            }
-        }
-    }
-    cp_async_wait<0>();
-}
-
 __global__ void __launch_bounds__(256)
 moe_gate_up_tc_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, const int* __restrict__ listed,
                       const int* __restrict__ tile_expert, bf16* __restrict__ y, int D, int F, int top, float limit,
@@ -467,7 +401,7 @@ extern "C" int hos_moe_route(const void* h, int dtype, const float* router, cons
                              cudaStream_t stream) {
     if (N <= 0) return 0;
     if (top <= 0 || top > n_out) HOS_REFUSE("moe_route: %d of %d router outputs cannot be chosen", top, n_out);
-    const size_t smem = (size_t)2 * n_out * sizeof(float);
+    const size_t smem = (size_t)(2 + 8) * n_out * sizeof(float);       // scores, flags, and a partial sum per warp (8 warps)
     if (smem > 48 * 1024) HOS_REFUSE("moe_route: %d router outputs are more than a block's shared memory holds", n_out);
     if (dtype == kBF16)
         launch_pdl(moe_route_kernel<bf16>, dim3(N), dim3(256), smem, stream, (const bf16*)h, router, correction, token_seq,

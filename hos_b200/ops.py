@@ -600,7 +600,7 @@ def latent_attn(q_lat: torch.Tensor, kc: Optional[torch.Tensor], cache: Optional
     or from the paged cache.  `n_splits` > 1: every row's keys are cut into that many shares that run side by side
     and are merged (few rows: decoding); `rows_per_block` > 1: neighbouring rows share the keys they read (prompts)."""
     _check(q_lat, "latent queries", torch.float32, 3)
-    _check(o_lat, "latent outputs", torch.float32, 3)
+    _check(o_lat, "latent outputs", (cache.k_pages if paged else kc).dtype, 3)
     n, heads, d = q_lat.shape
     if o_lat.shape != (n, heads, rank):
         raise KernelError("latent_attn: sizes disagree")

@@ -108,7 +108,7 @@ class LatentAttention(Mixer):
         ops.latent_prep(proj, H, self.dim, R, self.rot_dim, self.w_norm, self.eps, inv_freq, rot_dims, step, kc, q_lat, cache)
         # q'_h = W_uk_h^T q_h into the first `rank` numbers of every head's latent query
         ops.heads_product(proj, 0, proj.shape[1], self.dim + self.rot_dim, self.w_uk_t, q_lat, 0, H * D, D, n)
-        o_lat = torch.empty((n, H, R), dtype=torch.float32, device=h.device)
+        o_lat = torch.empty((n, H, R), dtype=h.dtype, device=h.device)      # what the value expansion reads
         nf = n if step.from_zero else step.fresh_tokens
         if nf > 0:
             shares, per_block = self.plan(nf, step)
