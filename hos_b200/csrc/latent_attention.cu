@@ -330,6 +330,223 @@ latent_attn_kernel(const float* __restrict__ q_lat, const T* __restrict__ kc, co
     }
 }
 
+// ---- latent_attn on the tensor cores (bfloat16 rows) -----------------------------------------------
+// The same walk with both products as m16n8k16 MMAs.  A block's 16 MMA rows are (2 rows of the step) x (8 heads).
+// The 32-bit absorbed query and the 32-bit softmax weights enter the tensor cores as two bfloat16 terms each
+// (value = hi + lo, 16 bits of mantissa between them; the keys and latents are bfloat16 as stored), and every
+// product is accumulated in 32-bit, so scores and weighted sums stay 32-bit quantities.  Key tiles of 32 positions
+// are copied as they lie (16-byte asynchronous copies, two stages, the next tile on its way during the
+// arithmetic); rows are padded so that ldmatrix finds no bank conflicts.  Scores: warp = (8 keys, half of the
+// row's numbers), the two halves added by the softmax warps (two MMA rows each, a lane per key).  Weighted sums:
+// every warp owns NT 8-wide column tiles of the latent.
+template <bool PAGED, int NT>
+__global__ void __launch_bounds__(kAttnThreads)
+latent_attn_tc_kernel(const float* __restrict__ q_lat, const bf16* __restrict__ kc, const bf16* __restrict__ k_pages,
+                      const int* __restrict__ page_table, int table_stride, int ring_pages,
+                      const float* __restrict__ sink, bf16* __restrict__ o_lat, float* __restrict__ part_acc,
+                      float* __restrict__ part_ml, const int* __restrict__ token_pos,
+                      const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
+                      const int* __restrict__ seq_slot, int row0, int row_end, int QT, int H, int R, int D, int Ds,
+                      float scale, int window) {
+    pdl_enter();
+    constexpr int kPs = 40, kSs = 36;           // row strides of the weight tiles (bf16) and the partial scores (f32)
+    extern __shared__ __align__(128) unsigned char raw[];
+    bf16* Qh = reinterpret_cast<bf16*>(raw);    // [16][Ds]
+    bf16* Ql = Qh + 16 * Ds;                    // [16][Ds]
+    bf16* Kt = Ql + 16 * Ds;                    // [2][kTK][Ds]
+    bf16* Ph = Kt + 2 * kTK * Ds;               // [16][kPs]
+    bf16* Pl = Ph + 16 * kPs;
+    float* Sp = reinterpret_cast<float*>(Pl + 16 * kPs);      // [2][16][kSs]
+    float* alpha = Sp + 2 * 16 * kSs;           // [16]
+    float* denom = alpha + 16;                  // [16]
+    __shared__ int row_seq[2], row_pos[2];
+    const int n0 = row0 + blockIdx.x * QT, h0 = blockIdx.y * kHG;
+    const int split = blockIdx.z, n_splits = gridDim.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nh = min(kHG, H - h0);
+    if (tid < 2) {
+        const int n = n0 + tid;
+        const bool in = tid < QT && n < row_end;
+        row_seq[tid] = in ? token_seq[n] : -1;
+        row_pos[tid] = in ? token_pos[n] : 0;
+    }
+    for (int i = tid; i < 16 * Ds; i += kAttnThreads) {
+        const int row = i / Ds, d = i - row * Ds, t = row >> 3, h = row & 7, n = n0 + t;
+        const float v = (t < QT && n < row_end && h < nh && d < D) ? q_lat[((size_t)n * H + h0 + h) * D + d] : 0.f;
+        const bf16 hi = __float2bfloat16_rn(v);
+        Qh[i] = hi;
+        Ql[i] = __float2bfloat16_rn(v - __bfloat162float(hi));
+    }
+    for (int i = tid; i < 2 * kTK * (Ds - D); i += kAttnThreads)       // the padding columns stay zero
+        Kt[(i / (Ds - D)) * Ds + D + i % (Ds - D)] = __float2bfloat16_rn(0.f);
+    __syncthreads();
+    // the softmax warps' running maxima and denominators: warp w keeps MMA rows 2w and 2w + 1
+    float m_run[2], l_run[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int row = 2 * warp + rr, t = row >> 3, h = row & 7;
+        m_run[rr] = -INFINITY;
+        l_run[rr] = 0.f;
+        if (h < nh && sink != nullptr && split == 0 && row_seq[t] >= 0) {
+            m_run[rr] = sink[h0 + h];
+            l_run[rr] = 1.f;
+        }
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[i][c] = 0.f;
+    const int groups = D >> 3;                  // 16-byte groups per stored row
+    const int ksteps = (Ds - 8) >> 4, khalf = warp >> 2, ntile = warp & 3;
+
+    for (int g0 = 0; g0 < 2;) {                 // the rows of one sequence at a time
+        const int seq = row_seq[g0];
+        int g1 = g0 + 1;
+        while (g1 < 2 && row_seq[g1] == seq) ++g1;
+        if (seq < 0) {
+            g0 = g1;
+            continue;
+        }
+        const int pos_first = row_pos[g0], pos_last = row_pos[g1 - 1];
+        const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+        const int tiles = (pos_last - lo + kTK) / kTK;
+        const int per = (tiles + n_splits - 1) / n_splits;
+        const int tile_lo = split * per, tile_hi = min(tiles, tile_lo + per);
+        const int seq_first = PAGED ? 0 : cu_seqlens[seq];
+        const int* table = PAGED ? page_table + (size_t)seq_slot[seq] * table_stride : nullptr;
+        const bf16* base = PAGED ? k_pages : kc;
+        auto issue = [&](int tile, int stage) {
+            const int p0 = lo + tile * kTK;
+            bf16* dst = Kt + stage * kTK * Ds;
+            for (int x = tid; x < kTK * groups; x += kAttnThreads) {
+                const int j = x / groups, gq = x - j * groups, p = p0 + j;
+                const bool ok = p <= pos_last;
+                size_t r = 0;
+                if (ok) {
+                    if (PAGED) {
+                        const int lp = p / kPageTokens;
+                        r = (size_t)table[ring_pages > 0 ? lp % ring_pages : lp] * kPageTokens + p % kPageTokens;
+                    } else {
+                        r = (size_t)(seq_first + p);
+                    }
+                }
+                cp_async16(dst + j * Ds + gq * 8, base + r * D + gq * 8, ok);
+            }
+        };
+        if (tile_lo < tile_hi) issue(tile_lo, 0);
+        cp_async_commit();
+        for (int tile = tile_lo; tile < tile_hi; ++tile) {
+            const int stage = (tile - tile_lo) & 1, p0 = lo + tile * kTK;
+            if (tile + 1 < tile_hi) issue(tile + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
+            const bf16* K = Kt + stage * kTK * Ds;
+            {   // scores of 8 keys over half of the row's numbers
+                float s4[4] = {0.f, 0.f, 0.f, 0.f};
+                const int half = ksteps >> 1;
+                for (int ks = khalf * half; ks < (khalf + 1) * half; ks += 2) {
+                    uint32_t w[4], a[4];
+                    ldmatrix_x4(w, smem_u32(K + (ntile * 8 + (lane & 7)) * Ds + ks * 16 + (lane >> 3) * 8));
+                    const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
+                    ldmatrix_x4(a, smem_u32(Qh + arow * Ds + ks * 16 + acol));
+                    mma_bf16(s4, a, w[0], w[1]);
+                    ldmatrix_x4(a, smem_u32(Ql + arow * Ds + ks * 16 + acol));
+                    mma_bf16(s4, a, w[0], w[1]);
+                    ldmatrix_x4(a, smem_u32(Qh + arow * Ds + (ks + 1) * 16 + acol));
+                    mma_bf16(s4, a, w[2], w[3]);
+                    ldmatrix_x4(a, smem_u32(Ql + arow * Ds + (ks + 1) * 16 + acol));
+                    mma_bf16(s4, a, w[2], w[3]);
+                }
+                float* out = Sp + khalf * 16 * kSs + ntile * 8 + (lane & 3) * 2;
+                *reinterpret_cast<float2*>(out + (lane >> 2) * kSs) = make_float2(s4[0], s4[1]);
+                *reinterpret_cast<float2*>(out + ((lane >> 2) + 8) * kSs) = make_float2(s4[2], s4[3]);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {    // softmax of MMA rows 2w, 2w + 1: a lane per key
+                const int row = 2 * warp + rr, t = row >> 3, h = row & 7;
+                const int kp = p0 + lane, pt = row_pos[t];
+                const bool live = t >= g0 && t < g1 && h < nh && kp <= pt && (window <= 0 || kp > pt - window);
+                const float sv = live ? (Sp[row * kSs + lane] + Sp[16 * kSs + row * kSs + lane]) * scale : -INFINITY;
+                const float m_new = fmaxf(m_run[rr], warp_max(sv));
+                const float p = live ? expf(sv - m_new) : 0.f;
+                const float a = m_new == -INFINITY ? 1.f : (m_run[rr] == -INFINITY ? 0.f : expf(m_run[rr] - m_new));
+                l_run[rr] = fmaf(l_run[rr], a, warp_sum(p));
+                m_run[rr] = m_new;
+                const bf16 hi = __float2bfloat16_rn(p);
+                Ph[row * kPs + lane] = hi;
+                Pl[row * kPs + lane] = __float2bfloat16_rn(p - __bfloat162float(hi));
+                if (lane == 0) alpha[row] = a;
+            }
+            __syncthreads();
+            {   // weighted sums: this warp's column tiles of the latent
+                const float a0 = alpha[lane >> 2], a1 = alpha[(lane >> 2) + 8];
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    acc[i][0] *= a0;
+                    acc[i][1] *= a0;
+                    acc[i][2] *= a1;
+                    acc[i][3] *= a1;
+                }
+                const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    uint32_t ph[4], pl[4];
+                    ldmatrix_x4(ph, smem_u32(Ph + arow * kPs + kk * 16 + (lane >> 4) * 8));
+                    ldmatrix_x4(pl, smem_u32(Pl + arow * kPs + kk * 16 + (lane >> 4) * 8));
+#pragma unroll
+                    for (int i = 0; i < NT; i += 2) {
+                        uint32_t v[4];
+                        ldmatrix_x4_trans(v, smem_u32(K + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * Ds +
+                                                      (warp * NT + i) * 8 + (lane >> 4) * 8));
+                        mma_bf16(acc[i], ph, v[0], v[1]);
+                        mma_bf16(acc[i], pl, v[0], v[1]);
+                        mma_bf16(acc[i + 1], ph, v[2], v[3]);
+                        mma_bf16(acc[i + 1], pl, v[2], v[3]);
+                    }
+                }
+            }
+            __syncthreads();                    // the stage is free for the tile after the next
+        }
+        cp_async_wait<0>();
+        g0 = g1;
+    }
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int row = 2 * warp + rr, t = row >> 3, h = row & 7, n = n0 + t;
+            denom[row] = l_run[rr];
+            if (n_splits > 1 && h < nh && t < QT && n < row_end) {
+                float* ml = part_ml + (((size_t)n * H + h0 + h) * n_splits + split) * 2;
+                ml[0] = m_run[rr];
+                ml[1] = l_run[rr];
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = (lane >> 2) + half * 8, t = row >> 3, h = row & 7, n = n0 + t;
+        if (t >= QT || n >= row_end || h >= nh) continue;
+        const float d = denom[row];
+        const bool live = row_seq[t] >= 0 && d > 0.f;
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int col = (warp * NT + i) * 8 + (lane & 3) * 2 + c;
+                if (col >= R) continue;
+                const float v = acc[i][half * 2 + c];
+                if (n_splits > 1) part_acc[(((size_t)n * H + h0 + h) * n_splits + split) * R + col] = v;
+                else o_lat[((size_t)n * H + h0 + h) * R + col] = __float2bfloat16_rn(live ? v / d : 0.f);
+            }
+        }
+    }
+}
+
 // o_lat[n][h] = sum_s e^{m_s - M} acc_s / sum_s e^{m_s - M} l_s over the shares s of the keys.
 template <typename T>
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
@@ -472,6 +689,48 @@ static int launch_attn_as(const float* q_lat, const void* kc, const void* k_page
     return rc;
 }
 
+template <bool PAGED, int NT>
+static int launch_attn_tc_as(const float* q_lat, const void* kc, const void* k_pages, const int* page_table, int table_stride,
+                             int ring_pages, const float* sink, void* o_lat, float* part_acc, float* part_ml, int n_splits,
+                             int QT, const int* token_pos, const int* token_seq, const int* cu_seqlens, const int* seq_slot,
+                             int row0, int rows, int H, int R, int D, float scale, int window, cudaStream_t stream) {
+    const int Ds = max((D + 63) / 64 * 64, 64 * NT) + 8;
+    const size_t smem = (size_t)(2 * 16 * Ds + 2 * kTK * Ds + 2 * 16 * 40) * 2 + (size_t)(2 * 16 * 36 + 32) * 4;
+    if (smem > 200 * 1024) return 1;                     // does not fit: the caller takes the other kernel
+    auto kernel = latent_attn_tc_kernel<PAGED, NT>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(kernel, dim3((rows + QT - 1) / QT, (H + kHG - 1) / kHG, n_splits), dim3(kAttnThreads), smem, stream, q_lat,
+               (const bf16*)kc, (const bf16*)k_pages, page_table, table_stride, ring_pages, sink, (bf16*)o_lat, part_acc,
+               part_ml, token_pos, token_seq, cu_seqlens, seq_slot, row0, row0 + rows, QT, H, R, D, Ds, scale, window);
+    int rc = check_launch("latent_attn");
+    if (rc == 0 && n_splits > 1) {
+        launch_pdl(latent_merge_kernel<bf16>, dim3(rows, H), dim3(128), 0, stream, (const float*)part_acc,
+                   (const float*)part_ml, (bf16*)o_lat, token_seq, row0, H, R, n_splits);
+        rc = check_launch("latent_merge");
+    }
+    return rc;
+}
+
+// 0: launched; 1: not a case for the tensor-core kernel; negative: an error.
+template <bool PAGED>
+static int launch_attn_tc(const float* q_lat, const void* kc, const void* k_pages, const int* page_table, int table_stride,
+                          int ring_pages, const float* sink, void* o_lat, float* part_acc, float* part_ml, int n_splits,
+                          int rows_per_block, const int* token_pos, const int* token_seq, const int* cu_seqlens,
+                          const int* seq_slot, int row0, int rows, int H, int R, int D, float scale, int window,
+                          cudaStream_t stream) {
+    const void* src = PAGED ? k_pages : kc;
+    if ((D & 7) != 0 || ((uintptr_t)src & 15) != 0 || R > 1024) return 1;
+    const int QT = (rows_per_block > 1 && n_splits == 1) ? 2 : 1;
+#define HOS_TC(NT) return launch_attn_tc_as<PAGED, NT>(q_lat, kc, k_pages, page_table, table_stride, ring_pages, sink, o_lat,   \
+                                                       part_acc, part_ml, n_splits, QT, token_pos, token_seq, cu_seqlens,    \
+                                                       seq_slot, row0, rows, H, R, D, scale, window, stream)
+    if (R <= 128) HOS_TC(2);
+    if (R <= 256) HOS_TC(4);
+    if (R <= 512) HOS_TC(8);
+    HOS_TC(16);
+#undef HOS_TC
+}
+
 // Rows per block: four where many rows share keys (prompts), fewer where the sums would not fit the registers;
 // one with shares of the keys (decoding).
 template <typename T, bool PAGED>
@@ -518,13 +777,14 @@ extern "C" int hos_latent_prep(const void* proj, int dtype, int proj_stride, int
 // Rows row0 .. row0 + rows - 1 of the step.  paged = 0: keys are the step's own rows `kc` (sequences
 // that start at position 0); paged = 1: keys from `k_pages` through the page table.  n_splits > 1: the keys of
 // every row are cut into that many shares (part_acc: [rows of the step][H][n_splits][R], part_ml: [..][n_splits][2]).
-// rows_per_block: 1, or more where neighbouring rows share their keys (prompts).
+// rows_per_block: 1, or more where neighbouring rows share their keys (prompts).  use_tensor_cores: bfloat16 rows
+// whose sizes fit take the MMA kernel (the 32-bit query and weights as two bfloat16 terms each); 0 keeps the FMA kernel.
 extern "C" int hos_latent_attn(int dtype, int paged, const float* q_lat, const void* kc, const void* k_pages,
                                const int* page_table, int table_stride, int ring_pages, const float* sink,
                                void* o_lat, float* part_acc, float* part_ml, int n_splits, int rows_per_block,
                                const int* token_pos, const int* token_seq, const int* cu_seqlens,
                                const int* seq_slot, int row0, int rows, int H, int R, int D, float scale, int window,
-                               cudaStream_t stream) {
+                               int use_tensor_cores, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (R > 4 * kAttnThreads) HOS_REFUSE("latent_attn: a latent of %d numbers is more than %d", R, 4 * kAttnThreads);
     if (R > D) HOS_REFUSE("latent_attn: the latent (%d) is longer than the row (%d)", R, D);
@@ -533,6 +793,15 @@ extern "C" int hos_latent_attn(int dtype, int paged, const float* q_lat, const v
 #define HOS_GO(T, PG) return launch_attn<T, PG>(q_lat, kc, k_pages, page_table, table_stride, ring_pages, sink, o_lat, part_acc, \
                                                  part_ml, n_splits, rows_per_block, token_pos, token_seq, cu_seqlens, seq_slot,   \
                                                  row0, rows, H, R, D, scale, window, stream)
+    if (dtype == kBF16 && use_tensor_cores) {
+        const int rc = paged ? launch_attn_tc<true>(q_lat, kc, k_pages, page_table, table_stride, ring_pages, sink, o_lat, part_acc,
+                                                    part_ml, n_splits, rows_per_block, token_pos, token_seq, cu_seqlens,
+                                                    seq_slot, row0, rows, H, R, D, scale, window, stream)
+                             : launch_attn_tc<false>(q_lat, kc, k_pages, page_table, table_stride, ring_pages, sink, o_lat, part_acc,
+                                                     part_ml, n_splits, rows_per_block, token_pos, token_seq, cu_seqlens,
+                                                     seq_slot, row0, rows, H, R, D, scale, window, stream);
+        if (rc <= 0) return rc;
+    }
     if (dtype == kBF16 && paged) HOS_GO(bf16, true);
     if (dtype == kBF16) HOS_GO(bf16, false);
     if (dtype == kF32 && paged) HOS_GO(float, true);

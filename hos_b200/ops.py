@@ -595,7 +595,7 @@ def latent_prep(proj: torch.Tensor, n_heads: int, dq: int, rank: int, rot: int, 
 
 def latent_attn(q_lat: torch.Tensor, kc: Optional[torch.Tensor], cache: Optional[PagedKVArgs], sink: Optional[torch.Tensor],
                 o_lat: torch.Tensor, step, row0: int, rows: int, rank: int, scale: float, window: Optional[int],
-                paged: bool, n_splits: int = 1, rows_per_block: int = 1) -> None:
+                paged: bool, n_splits: int = 1, rows_per_block: int = 1, tensor_cores: bool = True) -> None:
     """Rows row0 .. row0+rows-1 of the step: keys from `kc` (the step's own rows; sequences from position 0)
     or from the paged cache.  `n_splits` > 1: every row's keys are cut into that many shares that run side by side
     and are merged (few rows: decoding); `rows_per_block` > 1: neighbouring rows share the keys they read (prompts)."""
@@ -614,7 +614,8 @@ def latent_attn(q_lat: torch.Tensor, kc: Optional[torch.Tensor], cache: Optional
                   cache.table_stride if paged else 0, cache.ring_pages if paged else 0, _ptr(sink), _ptr(o_lat),
                   _ptr(part_acc), _ptr(part_ml), int(n_splits), int(rows_per_block),
                   _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot),
-                  int(row0), int(rows), heads, rank, d, float(scale), int(window) if window else 0, _stream())
+                  int(row0), int(rows), heads, rank, d, float(scale), int(window) if window else 0,
+                  1 if tensor_cores else 0, _stream())
 
 
 def heads_product(x: torch.Tensor, x_off: int, lda: int, a_head: int, w: torch.Tensor, out: torch.Tensor, out_off: int,
