@@ -318,7 +318,7 @@ def gemma_raw_like(z):
 
 
 def satapel_kernel_work(z, tokens, batch, ctx):
-    """Per launch of each of the design's own kernels: (bytes that must move, 32-bit FLOPs) for a prompt of
+    """Per launch of each of the design's own kernels: (bytes that must move, FLOPs of the mathematics) for a prompt of
     `tokens` tokens and for a decode step of `batch` sequences at length `ctx` (bfloat16 storage)."""
     H, D, R, W = z["heads"], z["rank"] + z["rot"], z["rank"], z["window"]
     pairs = sum(min(p + 1, W) for p in range(tokens))
@@ -343,8 +343,10 @@ def satapel_kernel_work(z, tokens, batch, ctx):
 
 def run_design_comparison(args) -> int:
     """Prompt and decode throughput of Satapel beside Gemma-2 at equal size, and where each of the design's own
-    kernels stands against its roofline (bytes over the measured copy rate, 32-bit FLOPs over the FMA pipes'
-    rate, whichever is larger).  One JSON line per size."""
+    kernels stands against its roofline: the larger of (bytes over the measured copy rate) and (the FLOPs of the
+    mathematics over the measured bfloat16 tensor rate; for the recurrence, which is 32-bit FMA work, over the FMA
+    pipes' rate).  The attention kernel issues twice its mathematics' FLOPs (two bfloat16 terms per 32-bit operand);
+    the fraction counts the mathematics only.  One JSON line per size."""
     import random
     import torch
     from hos_b200 import Engine, ops
@@ -405,7 +407,7 @@ def run_design_comparison(args) -> int:
                     row = {"calls": n, "ms": round(ms, 4)}
                     if fn in work:
                         by, fl = work[fn][phase]
-                        tensor = fn in ("hos_moe_gate_up", "hos_moe_down")        # bfloat16 products: tensor cores
+                        tensor = fn != "hos_wkv_scan"        # bfloat16 products and the attention: tensor cores
                         t_mem = by / (pk["hbm_gbs"] * 1e9)
                         t_fl = fl / ((pk["bf16_tflops"] if tensor else FP32_TFLOPS) * 1e12)
                         row["roofline_us_per_call"] = round(max(t_mem, t_fl) * 1e6, 2)

@@ -336,9 +336,10 @@ latent_attn_kernel(const float* __restrict__ q_lat, const T* __restrict__ kc, co
 // (value = hi + lo, 16 bits of mantissa between them; the keys and latents are bfloat16 as stored), and every
 // product is accumulated in 32-bit, so scores and weighted sums stay 32-bit quantities.  Key tiles of 32 positions
 // are copied as they lie (16-byte asynchronous copies, two stages, the next tile on its way during the
-// arithmetic); rows are padded so that ldmatrix finds no bank conflicts.  Scores: warp = (8 keys, half of the
-// row's numbers), the two halves added by the softmax warps (two MMA rows each, a lane per key).  Weighted sums:
-// every warp owns NT 8-wide column tiles of the latent.
+// arithmetic); rows are padded so that ldmatrix finds no bank conflicts.  Scores: every warp takes a share of the
+// row's numbers (16 at a time) for all 32 keys, so that a query fragment is loaded once for four key tiles; the
+// shares are added by the softmax warps (two MMA rows each, a lane per key).  Weighted sums: every warp owns NT
+// 8-wide column tiles of the latent.
 template <bool PAGED, int NT>
 __global__ void __launch_bounds__(kAttnThreads)
 latent_attn_tc_kernel(const float* __restrict__ q_lat, const bf16* __restrict__ kc, const bf16* __restrict__ k_pages,
@@ -356,8 +357,8 @@ latent_attn_tc_kernel(const float* __restrict__ q_lat, const bf16* __restrict__ 
     bf16* Kt = Ql + 16 * Ds;                    // [2][kTK][Ds]
     bf16* Ph = Kt + 2 * kTK * Ds;               // [16][kPs]
     bf16* Pl = Ph + 16 * kPs;
-    float* Sp = reinterpret_cast<float*>(Pl + 16 * kPs);      // [2][16][kSs]
-    float* alpha = Sp + 2 * 16 * kSs;           // [16]
+    float* Sp = reinterpret_cast<float*>(Pl + 16 * kPs);      // [warps][16][kSs] every warp's share of the scores
+    float* alpha = Sp + (kAttnThreads / 32) * 16 * kSs;       // [16]
     float* denom = alpha + 16;                  // [16]
     __shared__ int row_seq[2], row_pos[2];
     const int n0 = row0 + blockIdx.x * QT, h0 = blockIdx.y * kHG;
@@ -398,7 +399,7 @@ latent_attn_tc_kernel(const float* __restrict__ q_lat, const bf16* __restrict__ 
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[i][c] = 0.f;
     const int groups = D >> 3;                  // 16-byte groups per stored row
-    const int ksteps = (Ds - 8) >> 4, khalf = warp >> 2, ntile = warp & 3;
+    const int ksteps = (D + 15) >> 4;
 
     for (int g0 = 0; g0 < 2;) {                 // the rows of one sequence at a time
         const int seq = row_seq[g0];
@@ -443,25 +444,35 @@ latent_attn_tc_kernel(const float* __restrict__ q_lat, const bf16* __restrict__ 
             cp_async_wait<1>();
             __syncthreads();
             const bf16* K = Kt + stage * kTK * Ds;
-            {   // scores of 8 keys over half of the row's numbers
-                float s4[4] = {0.f, 0.f, 0.f, 0.f};
-                const int half = ksteps >> 1;
-                for (int ks = khalf * half; ks < (khalf + 1) * half; ks += 2) {
-                    uint32_t w[4], a[4];
-                    ldmatrix_x4(w, smem_u32(K + (ntile * 8 + (lane & 7)) * Ds + ks * 16 + (lane >> 3) * 8));
-                    const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
-                    ldmatrix_x4(a, smem_u32(Qh + arow * Ds + ks * 16 + acol));
-                    mma_bf16(s4, a, w[0], w[1]);
-                    ldmatrix_x4(a, smem_u32(Ql + arow * Ds + ks * 16 + acol));
-                    mma_bf16(s4, a, w[0], w[1]);
-                    ldmatrix_x4(a, smem_u32(Qh + arow * Ds + (ks + 1) * 16 + acol));
-                    mma_bf16(s4, a, w[2], w[3]);
-                    ldmatrix_x4(a, smem_u32(Ql + arow * Ds + (ks + 1) * 16 + acol));
-                    mma_bf16(s4, a, w[2], w[3]);
+            {   // scores of all 32 keys over this warp's share of the row's numbers (16 at a time, warp after warp)
+                float s4[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) s4[i][c] = 0.f;
+                const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, acol = (lane >> 4) * 8;
+                const int brow = (lane & 7) + (lane >> 4) * 8, bcol = ((lane >> 3) & 1) * 8;
+                for (int ks = warp; ks < ksteps; ks += kAttnThreads / 32) {
+                    uint32_t ah[4], al[4], w0[4], w1[4];
+                    ldmatrix_x4(ah, smem_u32(Qh + arow * Ds + ks * 16 + acol));
+                    ldmatrix_x4(al, smem_u32(Ql + arow * Ds + ks * 16 + acol));
+                    ldmatrix_x4(w0, smem_u32(K + brow * Ds + ks * 16 + bcol));
+                    ldmatrix_x4(w1, smem_u32(K + (16 + brow) * Ds + ks * 16 + bcol));
+                    mma_bf16(s4[0], ah, w0[0], w0[1]);
+                    mma_bf16(s4[1], ah, w0[2], w0[3]);
+                    mma_bf16(s4[2], ah, w1[0], w1[1]);
+                    mma_bf16(s4[3], ah, w1[2], w1[3]);
+                    mma_bf16(s4[0], al, w0[0], w0[1]);
+                    mma_bf16(s4[1], al, w0[2], w0[3]);
+                    mma_bf16(s4[2], al, w1[0], w1[1]);
+                    mma_bf16(s4[3], al, w1[2], w1[3]);
                 }
-                float* out = Sp + khalf * 16 * kSs + ntile * 8 + (lane & 3) * 2;
-                *reinterpret_cast<float2*>(out + (lane >> 2) * kSs) = make_float2(s4[0], s4[1]);
-                *reinterpret_cast<float2*>(out + ((lane >> 2) + 8) * kSs) = make_float2(s4[2], s4[3]);
+                float* out = Sp + warp * 16 * kSs + (lane & 3) * 2;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    *reinterpret_cast<float2*>(out + (lane >> 2) * kSs + i * 8) = make_float2(s4[i][0], s4[i][1]);
+                    *reinterpret_cast<float2*>(out + ((lane >> 2) + 8) * kSs + i * 8) = make_float2(s4[i][2], s4[i][3]);
+                }
             }
             __syncthreads();
 #pragma unroll
@@ -469,7 +480,10 @@ latent_attn_tc_kernel(const float* __restrict__ q_lat, const bf16* __restrict__ 
                 const int row = 2 * warp + rr, t = row >> 3, h = row & 7;
                 const int kp = p0 + lane, pt = row_pos[t];
                 const bool live = t >= g0 && t < g1 && h < nh && kp <= pt && (window <= 0 || kp > pt - window);
-                const float sv = live ? (Sp[row * kSs + lane] + Sp[16 * kSs + row * kSs + lane]) * scale : -INFINITY;
+                float dot = 0.f;
+#pragma unroll
+                for (int w = 0; w < kAttnThreads / 32; ++w) dot += Sp[(w * 16 + row) * kSs + lane];
+                const float sv = live ? dot * scale : -INFINITY;
                 const float m_new = fmaxf(m_run[rr], warp_max(sv));
                 const float p = live ? expf(sv - m_new) : 0.f;
                 const float a = m_new == -INFINITY ? 1.f : (m_run[rr] == -INFINITY ? 0.f : expf(m_run[rr] - m_new));
@@ -694,8 +708,8 @@ static int launch_attn_tc_as(const float* q_lat, const void* kc, const void* k_p
                              int ring_pages, const float* sink, void* o_lat, float* part_acc, float* part_ml, int n_splits,
                              int QT, const int* token_pos, const int* token_seq, const int* cu_seqlens, const int* seq_slot,
                              int row0, int rows, int H, int R, int D, float scale, int window, cudaStream_t stream) {
-    const int Ds = max((D + 63) / 64 * 64, 64 * NT) + 8;
-    const size_t smem = (size_t)(2 * 16 * Ds + 2 * kTK * Ds + 2 * 16 * 40) * 2 + (size_t)(2 * 16 * 36 + 32) * 4;
+    const int Ds = max((D + 15) / 16 * 16, 64 * NT) + 8;       // rows of 16-byte groups, an odd number of them
+    const size_t smem = (size_t)(2 * 16 * Ds + 2 * kTK * Ds + 2 * 16 * 40) * 2 + (size_t)(8 * 16 * 36 + 32) * 4;
     if (smem > 200 * 1024) return 1;                     // does not fit: the caller takes the other kernel
     auto kernel = latent_attn_tc_kernel<PAGED, NT>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
