@@ -12,6 +12,9 @@ back to the host, where the loop reads them one step late.  `prefill` is one pro
 step must read (every weight once, and the cache of the live sequences) to its time.
 `points` holds decoding at batch 1 and 64.  One JSON line is printed.
 
+`--design satapel` is another measurement (not the line above): prompt and decode throughput of the Satapel design at
+a few sizes beside Gemma-2 at equal size, and each of the design's kernels against its roofline; one JSON line per size.
+
 Random weights are made on the device; the cache of the decode measurements is filled with
 random keys and values instead of being computed by a prompt (a decode step reads the same
 bytes either way), and says so under config.cache_fill.

@@ -31,6 +31,9 @@ from .base import CallStore, KVNeed, Mixer, StepInfo, WeightSpec
 
 class LatentAttention(Mixer):
     graph_safe = True
+    # bfloat16 rows whose sizes fit run the MMA kernel (the 32-bit query and weights as two bfloat16 terms each);
+    # False keeps the FMA kernel everywhere (tests compare the two)
+    use_tensor_cores = True
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -113,7 +116,7 @@ class LatentAttention(Mixer):
         if nf > 0:
             shares, per_block = self.plan(nf, step)
             ops.latent_attn(q_lat, kc, None, self.sink, o_lat, step, 0, nf, R, self.scale, self.window, paged=False,
-                            n_splits=shares, rows_per_block=per_block)
+                            n_splits=shares, rows_per_block=per_block, tensor_cores=self.use_tensor_cores)
         if nf < n:
             if cache.ring_pages > 0 and not step.replayed:
                 room = cache.ring_pages * ops.PAGE_TOKENS - int(self.window) + 1
@@ -125,7 +128,7 @@ class LatentAttention(Mixer):
             rows = n - nf
             shares, per_block = self.plan(rows, step)
             ops.latent_attn(q_lat, None, cache, self.sink, o_lat, step, nf, rows, R, self.scale, self.window, paged=True,
-                            n_splits=shares, rows_per_block=per_block)
+                            n_splits=shares, rows_per_block=per_block, tensor_cores=self.use_tensor_cores)
         att = torch.empty((n, H * self.vdim), dtype=h.dtype, device=h.device)
         ops.heads_product(o_lat, 0, H * R, R, self.w_uv, att, 0, H * self.vdim, self.vdim, n)
         return linear.matmul(att, self.w_o)

@@ -327,3 +327,26 @@ def test_generation_through_the_command_line(folders):
                         "-p", ",".join(map(str, prompt))], stdout=subprocess.PIPE, stderr=subprocess.PIPE, timeout=900)
     assert p.returncode == 0, p.stderr.decode()[-2000:]
     assert p.stdout.decode().strip() == ",".join(map(str, prompt + want))
+
+
+def test_the_two_attention_kernels_agree_in_bfloat16(folders):
+    """The MMA kernel feeds the tensor cores the 32-bit query and weights as two bfloat16 terms each; the FMA kernel
+    multiplies them as they are.  On the same bfloat16 model the logits of a prompt, of pieces and of single tokens
+    differ by far less than bfloat16's own rounding."""
+    from hos_b200.parts.latent_attention import LatentAttention
+    vocab = CASES["C"][0]["vocab"]
+    seq = tokens(130, 200, vocab)
+    outs = []
+    for use in (True, False):
+        LatentAttention.use_tensor_cores = use
+        try:
+            r = _runner(folders["C"], "bfloat16")
+            (slot,) = r.admit(1)
+            got = [r.step([slot], [seq[:120]], [list(range(120))]), r.step([slot], [seq[120:150]], [list(range(30))])]
+            got += [r.step([slot], [[t]]) for t in seq[150:]]
+            outs.append(torch.cat(got).cpu())
+            r.release(slot)
+        finally:
+            LatentAttention.use_tensor_cores = True
+    e = row_errors(outs[0], outs[1])
+    assert float(e.median()) < 2e-3 and float((e < 1e-2).double().mean()) >= 0.9, f"median {float(e.median()):.2e}, worst {float(e.max()):.2e}"
