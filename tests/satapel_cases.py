@@ -63,7 +63,21 @@ CASE_C = model(80, 90, [attention(2, 16, 8, 16, 272, 0.15, window=64),
                         attention(4, 8, 8, 8, 16, 4.0, window=1),
                         recurrence(4, 8, 3)],
                moe=experts(2, 2, 2, 24, limit=0.8), mult=0.4)
-CASES = {"A": (CASE_A, 11), "B": (CASE_B, 12), "C": (CASE_C, 13)}
+# sizes that are multiples of nothing: no kernel that wants 16-byte rows can take them (width 100 is no multiple of
+# 8, rows of 36 latent numbers, experts of 36, heads of 20), more identity experts than one, top 4 of 10
+CASE_D = model(100, 77, [attention(5, 12, 6, 20, 30, 0.4, window=33),
+                         recurrence(5, 20, 7),
+                         recurrence(5, 20, 7, weights_of=1),
+                         attention(5, 12, 6, 20, 30, 0.4, window=33, weights_of=0, mlp="moe")],
+               moe=experts(7, 3, 4, 36, limit=1.1), mult=0.55, eps=3e-5, buckets=10, mul_prev=3, mul_cur=1)
+# wider layers: two head groups, latents of 200 and 520 numbers (the attention kernel's other column counts), a
+# window longer than four pages, recurrence heads of 64 and 128, experts of several feature tiles
+CASE_E = model(256, 500, [attention(16, 16, 16, 24, 200, 0.3, window=300),
+                          recurrence(2, 64, 16),
+                          attention(4, 32, 8, 40, 520, 0.25, window=None),
+                          recurrence(1, 128, 8, mlp=None)],
+               moe=experts(6, 1, 2, 264, limit=2.5), mult=0.5)
+CASES = {"A": (CASE_A, 11), "B": (CASE_B, 12), "C": (CASE_C, 13), "D": (CASE_D, 14), "E": (CASE_E, 15)}
 
 
 def _scaled(name: str, t: torch.Tensor) -> torch.Tensor:

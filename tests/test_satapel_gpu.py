@@ -38,7 +38,7 @@ def _oracle(folder, seqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
 def test_whole_prompts_of_unequal_lengths(folders, case, dtype):
     vocab = CASES[case][0]["vocab"]
     seqs = [tokens(i, n, vocab) for i, n in enumerate((1, 2, 37, 150))]      # 150: beyond two pages and every window
@@ -53,7 +53,7 @@ def test_whole_prompts_of_unequal_lengths(folders, case, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
 def test_a_prompt_then_token_by_token(folders, case, dtype):
     """Two requests decoded side by side through the replayed single-token step, across page borders (64, 128)
     and every window's edge; the shorter one leaves first."""
@@ -79,7 +79,44 @@ def test_a_prompt_then_token_by_token(folders, case, dtype):
     r.cache.check()
 
 
-@pytest.mark.parametrize("case, dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("C", "float32")])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_wider_layers_and_a_longer_prompt(folders, dtype):
+    """A prompt of 700 tokens, a piece of 90, then single tokens beside a second request that starts later.  In 32-bit
+    the rounding noise grows with the widths and the number of keys (as for the other architecture's test at real
+    widths): the median row stays within 1e-5 of the logits' size and every row within 1e-4, whichever path runs it
+    (the row that is furthest off is as far off in a whole prompt as at the head of a piece)."""
+    vocab = CASES["E"][0]["vocab"]
+    seqs = [tokens(140, 820, vocab), tokens(141, 75, vocab)]
+    want = _oracle(folders["E"], seqs)
+    r = _runner(folders["E"], dtype, max_seq_len=2048)
+    a, b = r.admit(2)
+    probe = list(range(0, 700, 7))
+    got = [r.step([a], [seqs[0][:700]], [probe]).cpu(), r.step([a], [seqs[0][700:790]], [list(range(90))]).cpu()]
+    got_b = [r.step([b, a], [seqs[1][:60], seqs[0][790:791]], [[59], [0]]).cpu()]
+    got.append(got_b[0][1:2])
+    got_b = [got_b[0][0:1]]
+    for k in range(15):
+        out = r.step([a, b], [[seqs[0][791 + k]], [seqs[1][60 + k]]]).cpu()
+        got.append(out[0:1])
+        got_b.append(out[1:2])
+    for k in range(15, 29):
+        got.append(r.step([a], [[seqs[0][791 + k]]]).cpu())
+    if dtype == "float32":
+        for g, x in ((torch.cat(got), torch.cat([want[0][probe], want[0][700:820]])), (torch.cat(got_b), want[1][59:75])):
+            e = row_errors(g, x)
+            assert float(e.median()) <= 1e-5 and float(e.max()) <= 1e-4, f"median {float(e.median()):.2e}, worst {float(e.max()):.2e}"
+    else:
+        # bfloat16 at these widths: a router choice that rounding flips moves a row by a third of its size, and a
+        # layer that sees all keys spreads it; only the median is asked for here (the 32-bit run above checks the
+        # mechanisms at these sizes, and the two attention kernels are compared with each other below)
+        e = row_errors(torch.cat(got), torch.cat([want[0][probe], want[0][700:820]]))
+        assert float(e.median()) <= 4e-2, f"median {float(e.median()):.2e}"
+    r.release(a)
+    r.release(b)
+    r.cache.check()
+
+
+@pytest.mark.parametrize("case, dtype", [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("C", "float32"), ("D", "bfloat16")])
 def test_a_prompt_in_pieces_of_many_sizes(folders, case, dtype):
     """Pieces down to two tokens and one, with a ring of pages that is only a little longer than the window, so
     that long pieces run as several passes."""
@@ -329,18 +366,19 @@ def test_generation_through_the_command_line(folders):
     assert p.stdout.decode().strip() == ",".join(map(str, prompt + want))
 
 
-def test_the_two_attention_kernels_agree_in_bfloat16(folders):
+@pytest.mark.parametrize("case", ["C"])
+def test_the_two_attention_kernels_agree_in_bfloat16(folders, case):
     """The MMA kernel feeds the tensor cores the 32-bit query and weights as two bfloat16 terms each; the FMA kernel
     multiplies them as they are.  On the same bfloat16 model the logits of a prompt, of pieces and of single tokens
     differ by far less than bfloat16's own rounding."""
     from hos_b200.parts.latent_attention import LatentAttention
-    vocab = CASES["C"][0]["vocab"]
+    vocab = CASES[case][0]["vocab"]
     seq = tokens(130, 200, vocab)
     outs = []
     for use in (True, False):
         LatentAttention.use_tensor_cores = use
         try:
-            r = _runner(folders["C"], "bfloat16")
+            r = _runner(folders[case], "bfloat16")
             (slot,) = r.admit(1)
             got = [r.step([slot], [seq[:120]], [list(range(120))]), r.step([slot], [seq[120:150]], [list(range(30))])]
             got += [r.step([slot], [[t]]) for t in seq[150:]]
@@ -350,3 +388,36 @@ def test_the_two_attention_kernels_agree_in_bfloat16(folders):
             LatentAttention.use_tensor_cores = True
     e = row_errors(outs[0], outs[1])
     assert float(e.median()) < 2e-3 and float((e < 1e-2).double().mean()) >= 0.9, f"median {float(e.median()):.2e}, worst {float(e.max()):.2e}"
+
+
+@pytest.mark.parametrize("heads, rank, rot, n, window, scale", [(16, 200, 16, 200, 300, 0.05), (8, 272, 8, 150, 64, 0.05),
+                                                                (3, 40, 12, 130, None, 0.3), (2, 520, 8, 70, 33, 0.05)])
+def test_the_attention_kernels_alone(heads, rank, rot, n, window, scale):
+    """Both kernels (MMA and FMA), one and several rows to a block, on random latent rows against float64: two head
+    groups, every count of column tiles, a latent too wide for the MMA kernel's shared memory (it steps aside), a
+    row size that is no multiple of 8.  The output is bfloat16: its rounding is the error."""
+    from hos_b200 import ops
+    from hos_b200.parts.base import StepInfo
+    torch.manual_seed(heads * 1000 + rank)
+    d = rank + rot
+    q = torch.randn(n, heads, d, device="cuda")
+    kc = torch.randn(n, d, device="cuda").to(torch.bfloat16)
+    sink = torch.randn(heads, device="cuda")
+    pos = torch.arange(n, dtype=torch.int32, device="cuda")
+    step = StepInfo(n, 1, None, pos, torch.zeros(n, dtype=torch.int32, device="cuda"),
+                    torch.tensor([0, n], dtype=torch.int32, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"),
+                    None, True, False, n, n)
+    k64, q64 = kc.double().cpu(), q.double().cpu()
+    s = torch.einsum("ihd,jd->hij", q64, k64) * scale
+    i, j = torch.arange(n)[:, None], torch.arange(n)[None]
+    seen = (i >= j) & ((i - j < window) if window else torch.ones(n, n, dtype=torch.bool))
+    s = s.masked_fill(~seen, float("-inf"))
+    p = torch.softmax(torch.cat([s, sink.double().cpu().view(heads, 1, 1).expand(heads, n, 1)], -1), -1)[..., :n]
+    want = torch.einsum("hij,jr->ihr", p, k64[:, :rank])
+    for tensor_cores in (True, False):
+        for per_block in (4, 1):
+            out = torch.empty(n, heads, rank, dtype=torch.bfloat16, device="cuda")
+            ops.latent_attn(q, kc, None, sink, out, step, 0, n, rank, scale, window, paged=False, n_splits=1,
+                            rows_per_block=per_block, tensor_cores=tensor_cores)
+            err = float((out.double().cpu() - want).abs().max() / want.abs().max())
+            assert err < 4e-3, f"tensor cores {tensor_cores}, {per_block} rows a block: {err:.2e}"
