@@ -8,14 +8,16 @@
 // and the value projection is applied after the weighted sum of latents:
 //     out_h(i) = W_uv_h  sum_j p_h(i, j) c_j.
 // So every head reads the same D numbers per key (one key/value "head" of size D whose value is
-// its first R numbers).  Scores, softmax and the weighted sums are 32-bit FMA work whatever the
-// storage type is.  Mask: causal with an optional window of the last `window` keys.  Optional
+// its first R numbers).  Scores, softmax and the weighted sums are 32-bit quantities whatever the
+// storage type is: 32-bit FMA work in latent_attn_kernel, two bfloat16 terms per 32-bit operand on the
+// tensor cores in latent_attn_tc_kernel (bfloat16 rows).  Mask: causal with an optional window of the last `window` keys.  Optional
 // sink: a learned number per head that joins the softmax's denominator as exp(sink), without a key
 // or a value and unscaled.
 //
-// Kernels: latent_prep (norm of c, rotations, cache write), latent_attn (keys from the step's own
-// rows for sequences that start at position 0, or from the paged cache), heads_product (the per-head
-// products W_uk_h^T q_h and W_uv_h o_h as one launch over all heads).
+// Kernels: latent_prep (norm of c, rotations, cache write), latent_attn and latent_attn_tc (keys from
+// the step's own rows for sequences that start at position 0, or from the paged cache), latent_merge
+// (the shares of a row's keys put together), heads_product and heads_product_tc (the per-head products
+// W_uk_h^T q_h and W_uv_h o_h as one launch over all heads).
 #include "common.cuh"
 #include "kv_layout.cuh"
 #include "mma_tile.cuh"

@@ -10,7 +10,8 @@ per head joins the softmax's denominator as exp(sink_h) (no key, no value, unsca
 Neither keys nor values are formed: the query absorbs W_uk (q'_h = W_uk_h^T q_h, `kv_rank`
 numbers) and W_uv is applied to the weighted sum of latents, so the attention kernel reads
 `kv_rank + rot_dim` numbers per key for all heads.  Everything between the projections (norm of
-c, angles, scores, softmax, weighted sums) is 32-bit.
+c, angles, scores, softmax, weighted sums) is 32-bit; with bfloat16 rows the two products run on the
+tensor cores with every 32-bit operand as two bfloat16 terms (csrc/latent_attention.cu).
 
 Cache: one keys-only group of row size kv_rank + rot_dim, a window ring if `window` is set.
 A sequence that starts at position 0 attends over the step's own rows; one that goes on (by
