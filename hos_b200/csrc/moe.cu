@@ -372,6 +372,89 @@ moe_down_tc_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, const
     }
 }
 
+// ---- a handful of rows (decoding at small batch) ---------------------------------------------------
+// With a few (row, choice) pairs a tile of 64 rows is nearly empty and there are too few tiles to fill the GPU.
+// These kernels take the pairs as they are: a block per (pair, 32 output features), a warp per 4 features, every
+// lane 16 bytes of a weight row at a time against the activation row in shared memory; the weights of an expert
+// that several pairs chose are read again from L2.  bfloat16, K a multiple of 8.
+constexpr int kFewFeatures = 32;
+
+__device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
+    const uint32_t x[4] = {a.x, a.y, a.z, a.w}, y[4] = {b.x, b.y, b.z, b.w};
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        s = fmaf(__uint_as_float(x[i] << 16), __uint_as_float(y[i] << 16), s);
+        s = fmaf(__uint_as_float(x[i] & 0xffff0000u), __uint_as_float(y[i] & 0xffff0000u), s);
+    }
+    return s;
+}
+
+// y[pair][F] = act(gate, up) of row pair / top under expert choice[pair]
+__global__ void __launch_bounds__(256)
+moe_gate_up_few_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, const int* __restrict__ choice,
+                       bf16* __restrict__ y, int D, int F, int top, int n_experts, float limit, float alpha) {
+    pdl_enter();
+    extern __shared__ __align__(128) unsigned char raw[];
+    uint4* row = reinterpret_cast<uint4*>(raw);                 // the activation row, 8 numbers a group
+    const int pair = blockIdx.y, e = choice[pair];
+    if (e < 0 || e >= n_experts) return;
+    const int groups = D >> 3, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(pair / top) * D);
+    for (int g = threadIdx.x; g < groups; g += 256) row[g] = src[g];
+    __syncthreads();
+    const bf16* Wg = W + (size_t)e * 2 * F * D;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int f = blockIdx.x * kFewFeatures + warp * 4 + q;
+        if (f >= F) break;
+        const uint4* g_row = reinterpret_cast<const uint4*>(Wg + (size_t)f * D);
+        const uint4* u_row = reinterpret_cast<const uint4*>(Wg + (size_t)(F + f) * D);
+        float sg = 0.f, su = 0.f;
+        for (int g = lane; g < groups; g += 32) {
+            const uint4 x = row[g];
+            sg += dot8(x, g_row[g]);
+            su += dot8(x, u_row[g]);
+        }
+        sg = warp_sum(sg);
+        su = warp_sum(su);
+        if (lane == 0) {
+            if (limit > 0.f) {
+                sg = fminf(sg, limit);
+                su = fminf(fmaxf(su, -limit), limit);
+            }
+            y[(size_t)pair * F + f] = from_float<bf16>(sg / (1.f + expf(-alpha * sg)) * (su + 1.f));
+        }
+    }
+}
+
+// pair_out[pair][D] = weight[pair] * (W_down[e] . y[pair])
+__global__ void __launch_bounds__(256)
+moe_down_few_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, const int* __restrict__ choice,
+                    const float* __restrict__ weight, float* __restrict__ pair_out, int D, int F, int n_experts) {
+    pdl_enter();
+    extern __shared__ __align__(128) unsigned char raw[];
+    uint4* row = reinterpret_cast<uint4*>(raw);
+    const int pair = blockIdx.y, e = choice[pair];
+    if (e < 0 || e >= n_experts) return;
+    const int groups = F >> 3, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint4* src = reinterpret_cast<const uint4*>(y + (size_t)pair * F);
+    for (int g = threadIdx.x; g < groups; g += 256) row[g] = src[g];
+    __syncthreads();
+    const bf16* Wd = W + (size_t)e * D * F;
+    const float wt = weight[pair];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int n = blockIdx.x * kFewFeatures + warp * 4 + q;
+        if (n >= D) break;
+        const uint4* w_row = reinterpret_cast<const uint4*>(Wd + (size_t)n * F);
+        float s = 0.f;
+        for (int g = lane; g < groups; g += 32) s += dot8(row[g], w_row[g]);
+        s = warp_sum(s);
+        if (lane == 0) pair_out[(size_t)pair * D + n] = s * wt;
+    }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ choice,
                                    const float* __restrict__ weight, const T* __restrict__ h, float* __restrict__ out,
@@ -485,4 +568,26 @@ extern "C" int hos_moe_combine(const float* pair_out, const int* choice, const f
     else
         HOS_REFUSE("moe_combine: unknown dtype %d", dtype);
     return check_launch("moe_combine");
+}
+
+// The same two products for a handful of pairs (see the kernels): y is [pairs][F] by pair id.  Returns 1 (and
+// launches nothing) where the sizes are not the kernels' (K no multiple of 8, rows that do not fit shared memory).
+extern "C" int hos_moe_gate_up_few(const void* h, const void* W, const int* choice, void* y, int n_pairs, int D, int F,
+                                   int top, int n_experts, float limit, float alpha, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (D % 8 || F % 8 || D * 2 > 96 * 1024 || ((uintptr_t)h | (uintptr_t)W | (uintptr_t)y) % 16) return 1;
+    if (D * 2 > 48 * 1024) cudaFuncSetAttribute(moe_gate_up_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, D * 2);
+    launch_pdl(moe_gate_up_few_kernel, dim3((F + kFewFeatures - 1) / kFewFeatures, n_pairs), dim3(256), (size_t)D * 2, stream,
+               (const bf16*)h, (const bf16*)W, choice, (bf16*)y, D, F, top, n_experts, limit, alpha);
+    return check_launch("moe_gate_up_few");
+}
+
+extern "C" int hos_moe_down_few(const void* y, const void* W, const int* choice, const float* weight, float* pair_out,
+                                int n_pairs, int D, int F, int n_experts, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (D % 8 || F % 8 || F * 2 > 96 * 1024 || ((uintptr_t)y | (uintptr_t)W) % 16) return 1;
+    if (F * 2 > 48 * 1024) cudaFuncSetAttribute(moe_down_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F * 2);
+    launch_pdl(moe_down_few_kernel, dim3((D + kFewFeatures - 1) / kFewFeatures, n_pairs), dim3(256), (size_t)F * 2, stream,
+               (const bf16*)y, (const bf16*)W, choice, weight, pair_out, D, F, n_experts);
+    return check_launch("moe_down_few");
 }

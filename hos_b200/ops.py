@@ -700,6 +700,26 @@ def moe_down(y, w, listed, tile_expert, weight, pair_out) -> None:
                   _ptr(pair_out), tile_expert.numel(), w.shape[1], w.shape[2], _stream())
 
 
+def moe_few(h, w_gate_up, w_down, choice, weight, y, pair_out, top: int, n_experts: int, limit: float, alpha: float) -> bool:
+    """Both expert products for a handful of (row, choice) pairs, without lists or tiles (decoding at small batch):
+    y [pairs, F] and pair_out [pairs, D] by pair id.  False: the sizes are not these kernels' and nothing ran."""
+    lib = blocks()
+    global launch_count
+    pairs, d, f = choice.numel(), h.shape[1], w_down.shape[2]
+    rc = lib.fn("hos_moe_gate_up_few")(_ptr(h), _ptr(w_gate_up), _ptr(choice), _ptr(y), pairs, d, f, int(top), int(n_experts),
+                                       float(limit), float(alpha), _stream())
+    if rc == 1:
+        return False
+    if rc == 0:
+        rc = lib.fn("hos_moe_down_few")(_ptr(y), _ptr(w_down), _ptr(choice), _ptr(weight), _ptr(pair_out), pairs, d, f,
+                                        int(n_experts), _stream())
+    launch_count += 2
+    if rc != 0:
+        msg = lib._last_error() if lib._last_error else b""
+        raise KernelError((msg or b"").decode(errors="replace") or "the few-rows expert products failed")
+    return True
+
+
 def moe_combine(pair_out, choice, weight, h, out, top: int, n_experts: int) -> None:
     n, d = h.shape
     blocks().call("hos_moe_combine", _ptr(pair_out), _ptr(choice), _ptr(weight), _ptr(h), dtype_code(h.dtype), _ptr(out),

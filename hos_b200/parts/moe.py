@@ -20,6 +20,9 @@ from ..registry import register_part
 from .base import FeedForward, StepInfo, WeightSpec
 
 
+FEW_PAIRS = 32          # up to this many (row, choice) pairs take the kernels without lists and tiles
+
+
 class RoutedExperts(FeedForward):
     graph_safe = True
 
@@ -70,15 +73,22 @@ class RoutedExperts(FeedForward):
         out = torch.empty((n, self.width), dtype=torch.float32, device=dev)
         pair_out = None
         if self.n_experts > 0:
-            # every expert's list is padded to whole tiles: at most this many tiles whatever the router chooses
-            max_tiles = min(pairs, self.n_experts) + pairs // tile
-            listed = torch.empty(max_tiles * tile, dtype=torch.int32, device=dev)
-            tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
-            ops.moe_align(choice, self.n_experts, listed, tile_expert)
-            y = torch.empty((max_tiles * tile, self.inner), dtype=h.dtype, device=dev)
-            ops.moe_gate_up(h, self.w_gate_up, listed, tile_expert, y, top, self.limit, self.alpha)
             pair_out = torch.empty((pairs, self.width), dtype=torch.float32, device=dev)
-            ops.moe_down(y, self.w_down, listed, tile_expert, weight, pair_out)
+            done = False
+            if pairs <= FEW_PAIRS and h.dtype == torch.bfloat16:
+                # a handful of pairs: a block per pair and slice of the features, no lists, no tiles
+                y = torch.empty((pairs, self.inner), dtype=h.dtype, device=dev)
+                done = ops.moe_few(h, self.w_gate_up, self.w_down, choice, weight, y, pair_out, top, self.n_experts,
+                                   self.limit, self.alpha)
+            if not done:
+                # every expert's list is padded to whole tiles: at most this many tiles whatever the router chooses
+                max_tiles = min(pairs, self.n_experts) + pairs // tile
+                listed = torch.empty(max_tiles * tile, dtype=torch.int32, device=dev)
+                tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+                ops.moe_align(choice, self.n_experts, listed, tile_expert)
+                y = torch.empty((max_tiles * tile, self.inner), dtype=h.dtype, device=dev)
+                ops.moe_gate_up(h, self.w_gate_up, listed, tile_expert, y, top, self.limit, self.alpha)
+                ops.moe_down(y, self.w_down, listed, tile_expert, weight, pair_out)
         ops.moe_combine(pair_out, choice, weight, h, out, top, self.n_experts)
         return out
 
