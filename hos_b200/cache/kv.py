@@ -43,7 +43,8 @@ class KVGroup:
         # zero-filled once: a page's unwritten rows are never selected by a mask, but they
         # are multiplied by zero weights, and 0 * NaN would not be 0
         self.k = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_entries)]
-        self.v = [None if need.keys_only else torch.zeros(shape, dtype=dtype, device=device) for _ in range(n_entries)]
+        v_shape = (n_pages, need.n_kv_heads, PAGE, need.v_head_dim or need.head_dim)
+        self.v = [None if need.keys_only else torch.zeros(v_shape, dtype=dtype, device=device) for _ in range(n_entries)]
         self.table_host = torch.zeros((n_slots, self.table_stride), dtype=torch.int32)
         self.table_dev = torch.zeros((n_slots, self.table_stride), dtype=torch.int32, device=device)
         self._slot_pages: Dict[int, List[int]] = {}
@@ -102,8 +103,9 @@ class KVGroup:
 
     def view(self, entry: int) -> ops.PagedKVArgs:
         return ops.PagedKVArgs(self.k[entry], self.v[entry], self.table_dev, self.ring_pages,
-                               self.need.n_kv_heads, self.need.head_dim)
+                               self.need.n_kv_heads, self.need.head_dim, self.need.v_head_dim or 0)
 
     def bytes_per_token(self) -> int:
         e = self.k[0].element_size()
-        return (1 if self.need.keys_only else 2) * self.n_entries * self.need.n_kv_heads * self.need.head_dim * e
+        per_head = self.need.head_dim + (0 if self.need.keys_only else (self.need.v_head_dim or self.need.head_dim))
+        return self.n_entries * self.need.n_kv_heads * per_head * e

@@ -20,6 +20,9 @@ Libraries and what needs them:
   blocks      models built from the other kinds of block: the hashed token-pair embedding, the
               parallel block's add-and-norms, attention over a latent cache, the matrix-state
               recurrence, the routed feed-forward
+  mixers      models with a norm after the residual sum, attention with a sink, chunks and a gate per
+              head over keys and values of unequal sizes, and the matrix-state recurrences with a
+              decay per head (constant, or per token with the delta rule and short convolutions)
 """
 from __future__ import annotations
 
@@ -47,6 +50,7 @@ _STATIC_LIBS: Dict[str, Tuple[List[str], List[str]]] = {
     "gemm_tc": (["gemm_tc.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "blocks": (["embed_pair.cu", "latent_attention.cu", "wkv.cu", "moe.cu"], []),
+    "mixers": (["postnorm.cu", "gated_attention.cu", "state_scan.cu"], []),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

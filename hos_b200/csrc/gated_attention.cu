@@ -1,0 +1,347 @@
+// Softmax attention whose keys and values may differ in size, with per-head query/key norms, a partial
+// rotation with scaled frequencies, a mask of chunks or of a window, a sink in the denominator and a gate
+// per head.  Everything between the projections and the output projection is 32-bit arithmetic.
+//
+// qk_prep: one block per token over the fused projection row [q | k | v | gate logits] (32-bit, biases added
+//   here): each query and key head is divided by its root mean square and multiplied by a weight shared by
+//   the heads, its first rot_dims numbers are rotated as neighbouring pairs (2i, 2i+1) by the angle
+//   position * freq[i], cosine and sine times `magnitude`; queries are written as 32-bit rows, keys and values
+//   (in the cache's type) to their places in the paged cache.
+// gated_attn: one warp per (token, query head, share of the keys).  A lane takes a key: 32 scores at a time, then
+//   the lanes turn to the value columns.  Keys j of position i: j <= i and, with chunks of size C,
+//   floor(j / C) = floor(i / C); with a window W, j > i - W.  The denominator also holds exp(sink[head]).
+//   The head's output is multiplied by the logistic function of its gate logit.  With more than one share the
+//   partial (maximum, sum, weighted values) go to a workspace and attn_merge adds them.
+#include "common.cuh"
+#include "kv_layout.cuh"
+
+namespace hos {
+
+struct PagedKV2 {            // keys [n_pages][n_kv][64][kd], values [n_pages][n_kv][64][vd]
+    void* k_pages;
+    void* v_pages;
+    const int* page_table;
+    int table_stride;
+    int ring_pages;
+    int n_kv_heads;
+    int kd, vd;
+};
+
+__device__ __forceinline__ int table_entry(const PagedKV2& c, int lp) { return c.ring_pages > 0 ? lp % c.ring_pages : lp; }
+
+constexpr int kPrepPL = 16;       // a head of up to 32 * 16 numbers in a warp's registers
+
+template <typename TC>
+__global__ void __launch_bounds__(128)
+qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias, const float* __restrict__ q_norm,
+               const float* __restrict__ k_norm, float eps, const float* __restrict__ freq, int rot_dims, float magnitude,
+               const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+               float* __restrict__ q_out, PagedKV2 cache, int H, int G, int kd, int vd) {
+    pdl_enter();
+    const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = token_seq[n];
+    const float* row = proj + (size_t)n * ld;
+    if (seq < 0) {
+        for (int i = threadIdx.x; i < H * kd; i += blockDim.x) q_out[(size_t)n * H * kd + i] = 0.f;
+        return;
+    }
+    const int pos = token_pos[n];
+    const float fpos = (float)pos;
+    const int slot = seq_slot[seq];
+    const int page = G > 0 ? cache.page_table[(size_t)slot * cache.table_stride + table_entry(cache, pos / kPageTokens)] : 0;
+    const int r = pos % kPageTokens;
+    // query heads 0..H-1, then key heads H..H+G-1
+    for (int item = warp; item < H + G; item += 4) {
+        const bool is_q = item < H;
+        const int col0 = item * kd;                      // q heads and k heads follow one another in the row
+        const float* nw = is_q ? q_norm : k_norm;
+        float v[kPrepPL];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < kPrepPL; ++i) {
+            const int d = lane + 32 * i;
+            v[i] = d < kd ? row[col0 + d] + (bias ? bias[col0 + d] : 0.f) : 0.f;
+            ss = fmaf(v[i], v[i], ss);
+        }
+        if (nw != nullptr) {
+            ss = warp_sum(ss);
+            const float inv = 1.f / sqrtf(ss / (float)kd + eps);
+#pragma unroll
+            for (int i = 0; i < kPrepPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < kd) v[i] = v[i] * inv * nw[d];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kPrepPL; ++i) {
+            const int d = lane + 32 * i;
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);       // the pair's partner: the lane beside
+            if (d < rot_dims && d < kd) {
+                float sn, cs;
+                sincosf(fpos * freq[d >> 1], &sn, &cs);
+                sn *= magnitude;
+                cs *= magnitude;
+                v[i] = (d & 1) ? fmaf(v[i], cs, other * sn) : fmaf(v[i], cs, -other * sn);
+            }
+        }
+        if (is_q) {
+            float* qo = q_out + ((size_t)n * H + item) * kd;
+#pragma unroll
+            for (int i = 0; i < kPrepPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < kd) qo[d] = v[i];
+            }
+        } else {
+            const int g = item - H;
+            TC* kp = (TC*)cache.k_pages + ((size_t)page * G + g) * (size_t)kPageTokens * kd;
+#pragma unroll
+            for (int i = 0; i < kPrepPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < kd) kp[kv_elem_offset(r, d, kd)] = from_float<TC>(v[i]);
+            }
+        }
+    }
+    if (G > 0) {
+        const int col0 = (H + G) * kd;
+        for (int i = threadIdx.x; i < G * vd; i += blockDim.x) {
+            const int g = i / vd, d = i % vd;
+            TC* vp = (TC*)cache.v_pages + ((size_t)page * G + g) * (size_t)kPageTokens * vd;
+            vp[kv_elem_offset(r, d, vd)] = from_float<TC>(row[col0 + i] + (bias ? bias[col0 + i] : 0.f));
+        }
+    }
+}
+
+constexpr int kAttnWarps = 4;
+constexpr int kMaxVPL = 16;       // value heads of up to 32 * 16 numbers
+
+// 8 numbers of a cache row, whatever the type
+__device__ __forceinline__ void load8(const float* p, float (&f)[8]) {
+    const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
+    const uint4 u = *(const uint4*)p;
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <typename TC, int VPL>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __restrict__ sink, const float* __restrict__ gate,
+                  long long gate_stride, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                  const int* __restrict__ seq_slot, void* __restrict__ out, int out_bf16, float* __restrict__ part_acc,
+                  float* __restrict__ part_ml, int n_splits, int n_tokens, int H, int G, int kd, int vd, float scale,
+                  int chunk, int window) {
+    pdl_enter();
+    extern __shared__ float qs_all[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * kAttnWarps + warp;
+    if (item >= (long long)n_tokens * H * n_splits) return;
+    const int split = (int)(item % n_splits);
+    const int h = (int)((item / n_splits) % H), n = (int)(item / ((long long)n_splits * H));
+    const int seq = token_seq[n];
+    const size_t orow = ((size_t)n * H + h) * vd;
+    if (seq < 0) {
+        if (n_splits == 1)
+            for (int d = lane; d < vd; d += 32) {
+                if (out_bf16) ((bf16*)out)[orow + d] = from_float<bf16>(0.f);
+                else ((float*)out)[orow + d] = 0.f;
+            }
+        else if (lane < 2) part_ml[(((size_t)n * H + h) * n_splits + split) * 2 + lane] = lane == 0 ? -INFINITY : 0.f;
+        return;
+    }
+    const int pos = token_pos[n];
+    const int g = h / (H / G);
+    int lo = 0;
+    if (chunk > 0) lo = pos / chunk * chunk;
+    if (window > 0) lo = max(lo, pos + 1 - window);
+    int hi = pos + 1;
+    if (n_splits > 1) {       // shares are runs of whole blocks of 32 keys
+        const int blocks = (hi - lo + 31) / 32, per = (blocks + n_splits - 1) / n_splits;
+        const int a = lo + split * per * 32;
+        hi = min(hi, a + per * 32);
+        lo = a;
+    }
+    float* qs = qs_all + warp * kd;
+    const float* qp = q + ((size_t)n * H + h) * kd;
+    for (int d = lane; d < kd; d += 32) qs[d] = qp[d];
+    __syncwarp();
+    const int slot = seq_slot[seq];
+    const int* table = cache.page_table + (size_t)slot * cache.table_stride;
+
+    // the sink takes part once: in the first share
+    const bool with_sink = sink != nullptr && split == 0;
+    float m = with_sink ? sink[h] : -INFINITY;
+    float l = with_sink ? 1.f : 0.f;
+    float acc[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+    const bool vec = (kd & 7) == 0;
+
+    for (int t0 = lo; t0 < hi; t0 += 32) {
+        const int t = t0 + lane;
+        float s = -INFINITY;
+        int my_page = 0;
+        if (t < hi) {
+            my_page = table[table_entry(cache, t / kPageTokens)];
+            const int r = t % kPageTokens;
+            const TC* kp = (const TC*)cache.k_pages + ((size_t)my_page * G + g) * (size_t)kPageTokens * kd;
+            float dot = 0.f;
+            if (vec) {
+                for (int c = 0; c < kd; c += 8) {
+                    float f[8];
+                    load8(kp + kv_elem_offset(r, c, kd), f);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) dot = fmaf(qs[c + e], f[e], dot);
+                }
+            } else {
+                for (int d = 0; d < kd; ++d) dot = fmaf(qs[d], to_float(kp[kv_elem_offset(r, d, kd)]), dot);
+            }
+            s = dot * scale;
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float corr = expf(m - m_new);          // m_new is finite here: the block holds one key at least
+        const float p = t < hi ? expf(s - m_new) : 0.f;
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[i] *= corr;
+        m = m_new;
+        const int cnt = min(32, hi - t0);
+        for (int j = 0; j < cnt; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            const int pg = __shfl_sync(0xffffffffu, my_page, j);
+            const int r = (t0 + j) % kPageTokens;
+            const TC* vp = (const TC*)cache.v_pages + ((size_t)pg * G + g) * (size_t)kPageTokens * vd;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < vd) acc[i] = fmaf(pj, to_float(vp[kv_elem_offset(r, d, vd)]), acc[i]);
+            }
+        }
+    }
+    if (n_splits > 1) {
+        const size_t pi = ((size_t)n * H + h) * n_splits + split;
+        if (lane == 0) {
+            part_ml[pi * 2] = m;
+            part_ml[pi * 2 + 1] = l;
+        }
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int d = lane + 32 * i;
+            if (d < vd) part_acc[pi * vd + d] = acc[i];
+        }
+        return;
+    }
+    float f = l > 0.f ? 1.f / l : 0.f;
+    if (gate != nullptr) f *= 1.f / (1.f + expf(-gate[(size_t)n * gate_stride + h]));
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < vd) {
+            if (out_bf16) ((bf16*)out)[orow + d] = from_float<bf16>(acc[i] * f);
+            else ((float*)out)[orow + d] = acc[i] * f;
+        }
+    }
+}
+
+// one warp per (token, head): the shares' sums under one maximum
+__global__ void __launch_bounds__(128)
+attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int n_splits,
+                  const float* __restrict__ gate, long long gate_stride, const int* __restrict__ token_seq,
+                  void* __restrict__ out, int out_bf16, int n_tokens, int H, int vd) {
+    pdl_enter();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)n_tokens * H) return;
+    const int n = (int)(item / H), h = (int)(item % H);
+    const float* ml = part_ml + (size_t)item * n_splits * 2;
+    float m = -INFINITY;
+    const bool live = token_seq[n] >= 0;
+    if (live)
+        for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
+    float l = 0.f;
+    if (live)
+        for (int s = 0; s < n_splits; ++s) l += ml[2 * s + 1] > 0.f ? ml[2 * s + 1] * expf(ml[2 * s] - m) : 0.f;
+    float f = l > 0.f ? 1.f / l : 0.f;
+    if (live && gate != nullptr) f *= 1.f / (1.f + expf(-gate[(size_t)n * gate_stride + h]));
+    for (int d = lane; d < vd; d += 32) {
+        float a = 0.f;
+        if (live)
+            for (int s = 0; s < n_splits; ++s)
+                if (ml[2 * s + 1] > 0.f) a = fmaf(part_acc[((size_t)item * n_splits + s) * vd + d], expf(ml[2 * s] - m), a);
+        if (out_bf16) ((bf16*)out)[(size_t)item * vd + d] = from_float<bf16>(a * f);
+        else ((float*)out)[(size_t)item * vd + d] = a * f;
+    }
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+// proj: float32 [N][ld], columns q (H * kd), then k (G * kd) and v (G * vd) if G > 0 (a call that reads another
+// call's cache passes G = 0 and projects neither), then whatever else the caller keeps there.  bias: the same
+// columns' biases or null.  q_norm / k_norm: [kd] or null.  freq: [rot_dims / 2] or null.
+extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const float* q_norm, const float* k_norm, float eps,
+                           const float* freq, int rot_dims, float magnitude, const int* token_pos, const int* token_seq,
+                           const int* seq_slot, float* q_out, void* k_pages, void* v_pages, int cache_dtype,
+                           const int* page_table, int table_stride, int ring_pages, int N, int H, int G, int kd, int vd,
+                           cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (kd <= 0 || kd > 32 * kPrepPL) HOS_REFUSE("qk_prep: heads of %d numbers are outside 1..%d", kd, 32 * kPrepPL);
+    if (freq == nullptr) rot_dims = 0;
+    if (rot_dims % 2 != 0 || rot_dims > kd) HOS_REFUSE("qk_prep: %d rotated numbers in heads of %d", rot_dims, kd);
+    PagedKV2 c{k_pages, v_pages, page_table, table_stride, ring_pages, G, kd, vd};
+    if (cache_dtype == kBF16)
+        launch_pdl(qk_prep_kernel<bf16>, dim3(N), dim3(128), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq, rot_dims,
+                   magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd);
+    else
+        launch_pdl(qk_prep_kernel<float>, dim3(N), dim3(128), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq, rot_dims,
+                   magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd);
+    return check_launch("qk_prep");
+}
+
+// q: float32 [N][H][kd].  out: [N][H][vd] of out_dtype.  gate: row n's logit of head h at gate[n * gate_stride + h], or
+// null.  sink: [H] or null.  chunk, window: 0 for none.  n_splits > 1: part_acc [N][H][n_splits][vd] and part_ml
+// [N][H][n_splits][2] float32 must be given.
+extern "C" int hos_gated_attn(const float* q, void* k_pages, void* v_pages, int cache_dtype, const int* page_table,
+                              int table_stride, int ring_pages, const float* sink, const float* gate, long long gate_stride,
+                              const int* token_pos, const int* token_seq, const int* seq_slot, void* out, int out_dtype,
+                              float* part_acc, float* part_ml, int n_splits, int N, int H, int G, int kd, int vd, float scale,
+                              int chunk, int window, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (G <= 0 || H % G != 0) HOS_REFUSE("gated_attn: %d heads are not a multiple of %d kv heads", H, G);
+    if (vd <= 0 || vd > 32 * kMaxVPL) HOS_REFUSE("gated_attn: value heads of %d numbers are outside 1..%d", vd, 32 * kMaxVPL);
+    if (n_splits < 1 || (n_splits > 1 && (part_acc == nullptr || part_ml == nullptr)))
+        HOS_REFUSE("gated_attn: %d shares need a workspace", n_splits);
+    const size_t smem = (size_t)kAttnWarps * kd * sizeof(float);
+    if (smem > 48 * 1024) HOS_REFUSE("gated_attn: heads of %d numbers do not fit", kd);
+    PagedKV2 c{k_pages, v_pages, page_table, table_stride, ring_pages, G, kd, vd};
+    const long long items = (long long)N * H * n_splits;
+    const unsigned blocks = (unsigned)((items + kAttnWarps - 1) / kAttnWarps);
+    const int out_bf16 = out_dtype == kBF16;
+#define HOS_GA(TC, VPL)                                                                                              \
+    launch_pdl(gated_attn_kernel<TC, VPL>, dim3(blocks), dim3(kAttnWarps * 32), smem, stream, q, c, sink, gate,      \
+               gate_stride, token_pos, token_seq, seq_slot, out, out_bf16, part_acc, part_ml, n_splits, N, H, G, kd, vd, \
+               scale, chunk, window)
+#define HOS_GA_T(TC)                                                                                                 \
+    do {                                                                                                             \
+        if (vd <= 32) HOS_GA(TC, 1);                                                                                 \
+        else if (vd <= 64) HOS_GA(TC, 2);                                                                            \
+        else if (vd <= 128) HOS_GA(TC, 4);                                                                           \
+        else if (vd <= 256) HOS_GA(TC, 8);                                                                           \
+        else HOS_GA(TC, 16);                                                                                         \
+    } while (0)
+    if (cache_dtype == kBF16) HOS_GA_T(bf16);
+    else HOS_GA_T(float);
+#undef HOS_GA_T
+#undef HOS_GA
+    int rc = check_launch("gated_attn");
+    if (rc != 0 || n_splits == 1) return rc;
+    launch_pdl(attn_merge_kernel, dim3((unsigned)(((long long)N * H + 3) / 4)), dim3(128), 0, stream, (const float*)part_acc,
+               (const float*)part_ml, n_splits, gate, gate_stride, token_seq, out, out_bf16, N, H, vd);
+    return check_launch("attn_merge");
+}

@@ -1,0 +1,140 @@
+// Row kernels of a block whose norm comes AFTER the residual sum, and of mixers that norm and gate
+// their heads' outputs.
+//
+// scale_add_norm: x <- RMSNorm(alpha * x + y; w, eps), x the 32-bit residual stream, y a branch's output
+//   (rows in any type, or 32-bit partial sums [parts][N][D] of a product that split K, added here in a
+//   fixed order).  The same launch also writes what reads the new x next: h = x in the products' type
+//   (the next branch reads x itself), or h = RMSNorm(x; w_next, eps_next) (the model's last norm).
+// cast_rows: h = x in the products' type (the first layer's input).
+// group_norm_gate: out[n][g][:] = o[n][g][:] / sqrt(mean_g(o^2) + eps) * w * act(gate[n][g][:]), the
+//   groups being heads (a weight shared by all heads) or the whole row (one group, a weight per column);
+//   act is the logistic function or x times it.  Statistics, weight and gate are 32-bit.
+#include "common.cuh"
+
+namespace hos {
+
+template <typename TY, typename TH>
+__global__ void __launch_bounds__(256)
+scale_add_norm_kernel(const TY* __restrict__ y, int n_parts, long long part_stride, float alpha, float* __restrict__ x,
+                      const float* __restrict__ w, float eps, TH* __restrict__ h, const float* __restrict__ w_next,
+                      float eps_next, int D) {
+    pdl_enter();
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float b = to_float(y[base + d]);
+        for (int p = 1; p < n_parts; ++p) b += to_float(y[(size_t)p * part_stride + base + d]);
+        const float s = fmaf(alpha, x[base + d], b);
+        row[d] = s;
+        ss = fmaf(s, s, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)D + eps);
+    float ss2 = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = row[d] * inv * w[d];
+        x[base + d] = v;
+        row[d] = v;
+        ss2 = fmaf(v, v, ss2);
+    }
+    if (h == nullptr) return;
+    if (w_next == nullptr) {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) h[base + d] = from_float<TH>(row[d]);
+        return;
+    }
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.f / sqrtf(ss2 / (float)D + eps_next);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) h[base + d] = from_float<TH>(row[d] * inv2 * w_next[d]);
+}
+
+template <typename TH>
+__global__ void cast_rows_kernel(const float* __restrict__ x, TH* __restrict__ h, long long n) {
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) h[i] = from_float<TH>(x[i]);
+}
+
+template <typename TH>
+__global__ void __launch_bounds__(128)
+group_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_per_group,
+                       const float* __restrict__ gate, long long gate_stride, int act, const int* __restrict__ token_seq,
+                       TH* __restrict__ out, float eps, int G, int gs) {
+    pdl_enter();
+    __shared__ float scratch[32];
+    const int n = blockIdx.x, g = blockIdx.y;
+    const size_t base = ((size_t)n * G + g) * gs;
+    if (token_seq != nullptr && token_seq[n] < 0) {        // padding: a defined row, nothing read
+        for (int d = threadIdx.x; d < gs; d += blockDim.x) out[base + d] = from_float<TH>(0.f);
+        return;
+    }
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) {
+        const float v = o[base + d];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+    const float* wg = w + (w_per_group ? 0 : (size_t)g * gs);
+    const float* gt = gate + (size_t)n * gate_stride + (size_t)g * gs;
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) {
+        const float z = gt[d];
+        const float s = 1.f / (1.f + expf(-z));
+        out[base + d] = from_float<TH>(o[base + d] * inv * wg[d] * (act == 1 ? z * s : s));
+    }
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+// y: [N][D] of y_dtype, or n_parts > 1 planes of float32 partial sums.  h (of h_dtype) may be null; with w_next
+// null it is x itself in that type, else the next norm of x.
+extern "C" int hos_scale_add_norm(const void* y, int y_dtype, int n_parts, float alpha, float* x, const float* w, float eps,
+                                  void* h, int h_dtype, const float* w_next, float eps_next, int N, int D,
+                                  cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (n_parts > 1 && y_dtype != kF32) HOS_REFUSE("scale_add_norm: partial sums must be float32");
+    const size_t smem = (size_t)D * sizeof(float);
+    if (smem > 200 * 1024) HOS_REFUSE("scale_add_norm: width %d does not fit a block's shared memory", D);
+    const long long plane = (long long)N * D;
+#define HOS_SAN(TY, TH)                                                                                              \
+    do {                                                                                                             \
+        if (smem > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(scale_add_norm_kernel<TY, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_pdl(scale_add_norm_kernel<TY, TH>, dim3(N), dim3(256), smem, stream, (const TY*)y, n_parts, plane, alpha, x, \
+                   w, eps, (TH*)h, w_next, eps_next, D);                                                             \
+    } while (0)
+    const bool hb = h != nullptr && h_dtype == kBF16;
+    if (y_dtype == kBF16 && hb) HOS_SAN(bf16, bf16);
+    else if (y_dtype == kBF16) HOS_SAN(bf16, float);
+    else if (hb) HOS_SAN(float, bf16);
+    else HOS_SAN(float, float);
+#undef HOS_SAN
+    return check_launch("scale_add_norm");
+}
+
+extern "C" int hos_cast_rows(const float* x, void* h, int h_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (h_dtype == kBF16) launch_pdl(cast_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (bf16*)h, n);
+    else launch_pdl(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (float*)h, n);
+    return check_launch("cast_rows");
+}
+
+// o: [N][G][gs] float32.  w: [gs] if w_per_group (one weight for every group) else [G][gs].  gate: row n's gate of
+// group g, column d at gate[n * gate_stride + g * gs + d].  act: 0 logistic, 1 x times logistic.
+extern "C" int hos_group_norm_gate(const float* o, const float* w, int w_per_group, const float* gate, long long gate_stride,
+                                   int act, const int* token_seq, void* out, int out_dtype, float eps, int N, int G, int gs,
+                                   cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (G <= 0 || gs <= 0 || G > 65535) HOS_REFUSE("group_norm_gate: %d groups of %d", G, gs);
+    if (out_dtype == kBF16)
+        launch_pdl(group_norm_gate_kernel<bf16>, dim3(N, G), dim3(128), 0, stream, o, w, w_per_group, gate, gate_stride, act,
+                   token_seq, (bf16*)out, eps, G, gs);
+    else
+        launch_pdl(group_norm_gate_kernel<float>, dim3(N, G), dim3(128), 0, stream, o, w, w_per_group, gate, gate_stride, act,
+                   token_seq, (float*)out, eps, G, gs);
+    return check_launch("group_norm_gate");
+}

@@ -1,0 +1,294 @@
+// Linear recurrences with a matrix state per head, S [dim keys][vdim values] in 32-bit, one kernel for two rules:
+//
+//   decay rule   S <- g S + k v^T                                o = S^T q     (g a constant per head)
+//   delta rule   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q  (g, beta per token and head)
+//
+// The read-out sees the current token's write.  A sequence's state lives per slot as S^T ([head][vdim][dim]: a
+// thread's run of rows of one column is contiguous), starts at zero (a sequence whose first row is position 0
+// ignores what the slot holds), and is carried from step to step.
+//
+// state_scan: one block per (sequence, head, run of value columns); a column of S is cut into R runs of DR rows,
+//   one thread each (R lanes side by side, so that sums over a column are shuffles); tokens in order, a chunk of
+//   them staged in shared memory at a time.  Columns are independent of one another in both rules.
+// conv_prep (the delta rule's inputs): per token, the short causal convolution over time of the q, k, v
+//   projections (per channel, `taps` wide, the last tap the current token's, the inputs before a step's first
+//   row from the slot's state), x sigmoid(x) of it, q and k divided by their length per head
+//   (sqrt(sum + 1e-6)), q times dim^-1/2; beta = logistic(b); g = exp(-exp(A_log) softplus(a + dt_bias)).
+// conv_keep: the last taps - 1 inputs of every sequence go to the slot's state.
+#include "common.cuh"
+
+namespace hos {
+
+constexpr int kScanChunk = 8;       // tokens staged at a time
+constexpr int kPad = 4;             // floats after every DR staged numbers: 16-byte reads of R neighbours miss each other's banks
+
+__device__ __forceinline__ float silu_precise(float x) { return x / (1.f + expf(-x)); }
+
+template <int DR, bool DELTA>
+__global__ void __launch_bounds__(256)
+state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long long ld,
+                  int silu_on_load, const float* __restrict__ g, long long g_ld, const float* __restrict__ beta,
+                  long long beta_ld, float* __restrict__ state, const int* __restrict__ token_pos,
+                  const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
+                  float* __restrict__ out, int H, int Gk, int dim, int vdim, int R, int CC) {
+    pdl_enter();
+    extern __shared__ __align__(16) float sm[];
+    const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * CC;
+    const int lo = cu_seqlens[seq], hi = cu_seqlens[seq + 1];
+    if (hi <= lo || token_seq[lo] < 0) return;
+    const int slot = seq_slot[seq];
+    const int kh = head / (H / Gk);
+    const int r = threadIdx.x % R, c = threadIdx.x / R;
+    const int col = col0 + c;
+    const bool live = c < CC && col < vdim;
+    const int dpad = R * (DR + kPad);
+    float* qs = sm;                              // [chunk][dpad]
+    float* ks = qs + kScanChunk * dpad;          // [chunk][dpad]
+    float* vs = ks + kScanChunk * dpad;          // [chunk][CC]
+    float* gs = vs + kScanChunk * CC;            // [chunk]
+    float* bs = gs + kScanChunk;                 // [chunk]
+    float* os = bs + kScanChunk;                 // [chunk][CC]
+
+    float S[DR];
+    float* st = state + (((size_t)slot * H + head) * vdim + (live ? col : 0)) * dim + r * DR;
+    const bool fresh = token_pos[lo] == 0;
+#pragma unroll
+    for (int i = 0; i < DR; ++i) S[i] = (!fresh && live && r * DR + i < dim) ? st[i] : 0.f;
+
+    for (int t0 = lo; t0 < hi; t0 += kScanChunk) {
+        const int nt = min(kScanChunk, hi - t0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * R * DR; idx += blockDim.x) {
+            const int t = idx / (R * DR), d = idx % (R * DR);
+            float qv = 0.f, kv = 0.f;
+            if (d < dim) {
+                qv = q[(size_t)(t0 + t) * ld + kh * dim + d];
+                kv = k[(size_t)(t0 + t) * ld + kh * dim + d];
+                if (silu_on_load) {
+                    qv = silu_precise(qv);
+                    kv = silu_precise(kv);
+                }
+            }
+            const int at = t * dpad + d + (d / DR) * kPad;
+            qs[at] = qv;
+            ks[at] = kv;
+        }
+        for (int idx = threadIdx.x; idx < nt * CC; idx += blockDim.x) {
+            const int t = idx / CC, cc = idx % CC;
+            float vv = col0 + cc < vdim ? v[(size_t)(t0 + t) * ld + head * vdim + col0 + cc] : 0.f;
+            if (silu_on_load) vv = silu_precise(vv);
+            vs[idx] = vv;
+        }
+        if (threadIdx.x < nt) {
+            gs[threadIdx.x] = g[(size_t)(t0 + threadIdx.x) * g_ld + head];
+            bs[threadIdx.x] = DELTA ? beta[(size_t)(t0 + threadIdx.x) * beta_ld + head] : 1.f;
+        }
+        __syncthreads();
+        {       // every thread walks (a warp's shuffles want all its lanes); only live columns are written
+            for (int t = 0; t < nt; ++t) {
+                const float4* k4 = (const float4*)(ks + t * dpad + r * (DR + kPad));
+                const float4* q4 = (const float4*)(qs + t * dpad + r * (DR + kPad));
+                const float gt = gs[t];
+                float u = c < CC ? vs[t * CC + c] : 0.f;
+                if (DELTA) {
+                    float dot = 0.f;
+#pragma unroll
+                    for (int i = 0; i < DR / 4; ++i) {
+                        const float4 kk = k4[i];
+                        S[4 * i] *= gt; S[4 * i + 1] *= gt; S[4 * i + 2] *= gt; S[4 * i + 3] *= gt;
+                        dot = fmaf(S[4 * i], kk.x, dot);
+                        dot = fmaf(S[4 * i + 1], kk.y, dot);
+                        dot = fmaf(S[4 * i + 2], kk.z, dot);
+                        dot = fmaf(S[4 * i + 3], kk.w, dot);
+                    }
+                    for (int o = 1; o < R; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                    u = bs[t] * (u - dot);
+                }
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < DR / 4; ++i) {
+                    const float4 kk = k4[i], qq = q4[i];
+                    if (DELTA) {
+                        S[4 * i] = fmaf(kk.x, u, S[4 * i]);
+                        S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);
+                        S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);
+                        S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);
+                    } else {
+                        S[4 * i] = fmaf(gt, S[4 * i], kk.x * u);
+                        S[4 * i + 1] = fmaf(gt, S[4 * i + 1], kk.y * u);
+                        S[4 * i + 2] = fmaf(gt, S[4 * i + 2], kk.z * u);
+                        S[4 * i + 3] = fmaf(gt, S[4 * i + 3], kk.w * u);
+                    }
+                    acc = fmaf(S[4 * i], qq.x, acc);
+                    acc = fmaf(S[4 * i + 1], qq.y, acc);
+                    acc = fmaf(S[4 * i + 2], qq.z, acc);
+                    acc = fmaf(S[4 * i + 3], qq.w, acc);
+                }
+                for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (r == 0 && c < CC) os[t * CC + c] = acc;
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * CC; idx += blockDim.x) {
+            const int t = idx / CC, cc = idx % CC;
+            if (col0 + cc < vdim) out[((size_t)(t0 + t) * H + head) * vdim + col0 + cc] = os[idx];
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DR; ++i)
+            if (r * DR + i < dim) st[i] = S[i];
+    }
+}
+
+constexpr int kMaxTaps = 16;
+
+// raw: float32 [N][ld]: q (Gk * dim) | k (Gk * dim) | v (H * vdim) | b (H) | a (H) | ... ; conv_w: [C][taps] over
+// the first C = 2 Gk dim + H vdim columns; conv_state: [slots][taps - 1][C], row j the input taps - 1 - j tokens back.
+__global__ void __launch_bounds__(256)
+conv_prep_kernel(const float* __restrict__ raw, long long ld, const float* __restrict__ conv_w, int taps,
+                 const float* __restrict__ conv_state, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                 const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
+                 const int* __restrict__ seq_slot, float* __restrict__ act, float* __restrict__ beta_out,
+                 float* __restrict__ g_out, int H, int Gk, int dim, int vdim) {
+    pdl_enter();
+    extern __shared__ float qk[];                // [2 Gk dim] after the activation
+    __shared__ float inv_len[64];
+    const int n = blockIdx.x;
+    const int seq = token_seq[n];
+    const int QK = 2 * Gk * dim, C = QK + H * vdim;
+    float* arow = act + (size_t)n * C;
+    if (seq < 0) {
+        for (int i = threadIdx.x; i < C; i += blockDim.x) arow[i] = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            beta_out[(size_t)n * H + i] = 0.f;
+            g_out[(size_t)n * H + i] = 1.f;
+        }
+        return;
+    }
+    const int r0 = cu_seqlens[seq];
+    const bool fresh = token_pos[r0] == 0;
+    const float* keep = conv_state + (size_t)seq_slot[seq] * (taps - 1) * C;
+    for (int ch = threadIdx.x; ch < C; ch += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = n - (taps - 1) + j;          // the row of this step that holds the input, if it is one
+            float x = 0.f;
+            if (src >= r0) x = raw[(size_t)src * ld + ch];
+            else if (!fresh) x = keep[(size_t)((taps - 1) + (src - r0)) * C + ch];
+            acc = fmaf(conv_w[(size_t)ch * taps + j], x, acc);
+        }
+        const float y = silu_precise(acc);
+        if (ch < QK) qk[ch] = y;
+        else arow[ch] = y;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int hd0 = 0; hd0 < 2 * Gk; hd0 += 64) {         // the heads' lengths, a warp per head
+        for (int hd = hd0 + warp; hd < min(2 * Gk, hd0 + 64); hd += nwarps) {
+            float ss = 0.f;
+            for (int d = lane; d < dim; d += 32) ss = fmaf(qk[hd * dim + d], qk[hd * dim + d], ss);
+            ss = warp_sum(ss);
+            if (lane == 0) inv_len[hd - hd0] = (1.f / sqrtf(ss + 1e-6f)) * (hd < Gk ? 1.f / sqrtf((float)dim) : 1.f);
+        }
+        __syncthreads();
+        for (int i = hd0 * dim + threadIdx.x; i < min(2 * Gk, hd0 + 64) * dim; i += blockDim.x)
+            arow[i] = qk[i] * inv_len[i / dim - hd0];
+        __syncthreads();
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float b = raw[(size_t)n * ld + C + h], a = raw[(size_t)n * ld + C + H + h] + dt_bias[h];
+        beta_out[(size_t)n * H + h] = 1.f / (1.f + expf(-b));
+        const float sp = a > 20.f ? a : log1pf(expf(a));
+        g_out[(size_t)n * H + h] = expf(-expf(a_log[h]) * sp);
+    }
+}
+
+__global__ void conv_keep_kernel(const float* __restrict__ raw, long long ld, int taps, float* __restrict__ conv_state,
+                                 const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int C) {
+    pdl_enter();
+    const int seq = blockIdx.y;
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r0 = cu_seqlens[seq], r1 = cu_seqlens[seq + 1];
+    if (ch >= C || r1 <= r0 || token_seq[r0] < 0) return;
+    const bool fresh = token_pos[r0] == 0;
+    float* keep = conv_state + (size_t)seq_slot[seq] * (taps - 1) * C;
+    float nv[kMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) {
+        if (j < taps - 1) {
+            const int src = r1 - (taps - 1) + j;
+            nv[j] = src >= r0 ? raw[(size_t)src * ld + ch] : (fresh ? 0.f : keep[(size_t)((taps - 1) + (src - r0)) * C + ch]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j)
+        if (j < taps - 1) keep[(size_t)j * C + ch] = nv[j];
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+// q, k: rows of Gk heads of `dim` numbers; v: rows of H heads of `vdim`; all float32 with `ld` numbers between rows.
+// g: [.][H] with g_ld between rows (0: one row of constants).  beta: null for the decay rule.  state: [slots][H][vdim][dim].
+// out: float32 [N][H][vdim].
+extern "C" int hos_state_scan(const float* q, const float* k, const float* v, long long ld, int silu_on_load, const float* g,
+                              long long g_ld, const float* beta, long long beta_ld, float* state, const int* token_pos,
+                              const int* token_seq, const int* cu_seqlens, const int* seq_slot, float* out, int n_seqs, int H,
+                              int Gk, int dim, int vdim, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (Gk <= 0 || H % Gk != 0) HOS_REFUSE("state_scan: %d heads are not a multiple of %d key heads", H, Gk);
+    if (dim <= 0 || dim > 1024 || vdim <= 0) HOS_REFUSE("state_scan: heads of %d x %d", dim, vdim);
+    const int DR = dim <= 16 ? 4 : (dim <= 64 ? 8 : (dim <= 512 ? 16 : 32));
+    int R = 1;
+    while (R * DR < dim) R <<= 1;
+    int CC = 256 / R;
+    if (CC > vdim) CC = vdim;
+    const int threads = (CC * R + 31) / 32 * 32;
+    const int dpad = R * (DR + kPad);
+    const size_t smem = (size_t)(2 * kScanChunk * dpad + 2 * kScanChunk * CC + 2 * kScanChunk) * sizeof(float);
+    const dim3 grid(n_seqs, H, (vdim + CC - 1) / CC);
+    const bool delta = beta != nullptr;
+#define HOS_SCAN(DRv, DL)                                                                                            \
+    launch_pdl(state_scan_kernel<DRv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, silu_on_load, g, g_ld, beta, \
+               beta_ld, state, token_pos, token_seq, cu_seqlens, seq_slot, out, H, Gk, dim, vdim, R, CC)
+#define HOS_SCAN_D(DRv)                                                                                              \
+    do {                                                                                                             \
+        if (delta) HOS_SCAN(DRv, true);                                                                              \
+        else HOS_SCAN(DRv, false);                                                                                   \
+    } while (0)
+    if (DR == 4) HOS_SCAN_D(4);
+    else if (DR == 8) HOS_SCAN_D(8);
+    else if (DR == 16) HOS_SCAN_D(16);
+    else HOS_SCAN_D(32);
+#undef HOS_SCAN_D
+#undef HOS_SCAN
+    return check_launch("state_scan");
+}
+
+// act: float32 [N][2 Gk dim + H vdim] (q, k, v after convolution, activation and lengths); beta_out, g_out: [N][H].
+extern "C" int hos_conv_prep(const float* raw, long long ld, const float* conv_w, int taps, const float* conv_state,
+                             const float* a_log, const float* dt_bias, const int* token_pos, const int* token_seq,
+                             const int* cu_seqlens, const int* seq_slot, float* act, float* beta_out, float* g_out, int N,
+                             int H, int Gk, int dim, int vdim, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (taps < 1 || taps > kMaxTaps) HOS_REFUSE("conv_prep: %d taps are outside 1..%d", taps, kMaxTaps);
+    const size_t smem = (size_t)2 * Gk * dim * sizeof(float);
+    if (smem > 160 * 1024) HOS_REFUSE("conv_prep: %d query and key channels do not fit", 2 * Gk * dim);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(conv_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(conv_prep_kernel, dim3(N), dim3(256), smem, stream, raw, ld, conv_w, taps, conv_state, a_log, dt_bias,
+               token_pos, token_seq, cu_seqlens, seq_slot, act, beta_out, g_out, H, Gk, dim, vdim);
+    return check_launch("conv_prep");
+}
+
+extern "C" int hos_conv_keep(const float* raw, long long ld, int taps, float* conv_state, const int* token_pos,
+                             const int* token_seq, const int* cu_seqlens, const int* seq_slot, int n_seqs, int C,
+                             cudaStream_t stream) {
+    if (n_seqs <= 0 || taps <= 1) return 0;
+    if (taps > kMaxTaps) HOS_REFUSE("conv_keep: %d taps are outside 1..%d", taps, kMaxTaps);
+    launch_pdl(conv_keep_kernel, dim3((C + 127) / 128, n_seqs), dim3(128), 0, stream, raw, ld, taps, conv_state, token_pos,
+               token_seq, cu_seqlens, seq_slot, C);
+    return check_launch("conv_keep");
+}

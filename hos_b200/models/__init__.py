@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers them."""
-from . import gemma2, satapel  # noqa: F401
+from . import gemma2, satapel, vagonex  # noqa: F401

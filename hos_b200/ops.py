@@ -274,10 +274,15 @@ class PagedKVArgs:
     ring_pages: int              # 0: all keys kept; > 0: ring of that many pages
     n_kv_heads: int
     head_dim: int
+    v_head_dim: int = 0          # 0: values are as wide as keys
 
     @property
     def table_stride(self) -> int:
         return self.page_table.shape[1]
+
+    @property
+    def v_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 # ---- element-wise and norms ------------------------------------------------------------
@@ -724,3 +729,143 @@ def moe_combine(pair_out, choice, weight, h, out, top: int, n_experts: int) -> N
     n, d = h.shape
     blocks().call("hos_moe_combine", _ptr(pair_out), _ptr(choice), _ptr(weight), _ptr(h), dtype_code(h.dtype), _ptr(out),
                   n, d, int(top), int(n_experts), _stream())
+
+
+# ---- a norm after the sum, gated attention with a sink, matrix-state scans (csrc/postnorm.cu, gated_attention.cu,
+# ---- state_scan.cu) ----------------------------------------------------------------------------------------------
+_mixers: Optional[Library] = None
+ACT_LOGISTIC, ACT_X_LOGISTIC = 0, 1
+
+
+def mixers() -> Library:
+    global _mixers
+    if _mixers is None:
+        _mixers = Library("mixers")
+    return _mixers
+
+
+def scale_add_norm(y: torch.Tensor, alpha: float, x: torch.Tensor, w: torch.Tensor, eps: float,
+                   h: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None, eps_next: float = 0.0) -> None:
+    """x <- RMSNorm(alpha * x + y; w, eps).  y: [N, D], or [parts, N, D] float32 partial sums.  With `h`: h = the new x
+    in h's type, or, with `w_next`, RMSNorm(x; w_next, eps_next)."""
+    _check(x, "residual stream", torch.float32, 2)
+    _check(y, "branch output")
+    _check(w, "norm weight", torch.float32, 1)
+    n, d = x.shape
+    if y.dim() not in (2, 3) or tuple(y.shape[-2:]) != (n, d) or w.shape[0] != d:
+        raise KernelError("scale_add_norm: sizes disagree")
+    if h is not None:
+        _check(h, "next input", None, 2)
+        if h.shape != x.shape or (w_next is not None and w_next.shape[0] != d):
+            raise KernelError("scale_add_norm: sizes of the next input disagree")
+    mixers().call("hos_scale_add_norm", _ptr(y), dtype_code(y.dtype), y.shape[0] if y.dim() == 3 else 1, float(alpha),
+                  _ptr(x), _ptr(w), float(eps), _ptr(h), dtype_code(h.dtype) if h is not None else 0, _ptr(w_next),
+                  float(eps_next), n, d, _stream())
+
+
+def cast_rows(x: torch.Tensor, h: torch.Tensor) -> None:
+    _check(x, "rows", torch.float32)
+    _check(h, "rows in the products' type")
+    if h.shape != x.shape:
+        raise KernelError("cast_rows: sizes disagree")
+    mixers().call("hos_cast_rows", _ptr(x), _ptr(h), dtype_code(h.dtype), x.numel(), _stream())
+
+
+def group_norm_gate(o: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, gate_col: int, act: int, token_seq,
+                    out: torch.Tensor, eps: float, groups: int, group_size: int) -> None:
+    """out[n, g, :] = o[n, g, :] / rms * w * act(gate[n, gate_col + g * group_size + :]); w: [group_size] (shared by
+    the groups) or [groups * group_size]."""
+    _check(o, "mixer output", torch.float32, 2)
+    _check(gate, "gate rows", torch.float32, 2)
+    _check(w, "norm weight", torch.float32, 1)
+    n = o.shape[0]
+    if o.shape[1] != groups * group_size or out.shape != o.shape or w.shape[0] not in (group_size, groups * group_size) \
+            or gate.shape[0] != n or gate_col + groups * group_size > gate.shape[1]:
+        raise KernelError("group_norm_gate: sizes disagree")
+    shared = 1 if (w.shape[0] == group_size and groups > 1) else 0
+    mixers().call("hos_group_norm_gate", _ptr(o), _ptr(w), shared,
+                  ctypes.c_void_p(gate.data_ptr() + gate_col * 4), gate.shape[1], int(act), _ptr(token_seq), _ptr(out),
+                  dtype_code(out.dtype), float(eps), n, int(groups), int(group_size), _stream())
+
+
+def qk_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+            eps: float, freq: Optional[torch.Tensor], rot_dims: int, magnitude: float, step, q_out: torch.Tensor,
+            cache: PagedKVArgs, n_heads: int, n_kv: int, kd: int, vd: int) -> None:
+    """proj: float32 [N, >= H kd + G (kd + vd)] = [q | k | v | ...] (G = n_kv; 0: a call that stores nothing).  Adds the
+    biases, norms and rotates the q and k heads, writes q_out float32 [N, H, kd] and stores k, v in the cache."""
+    _check(proj, "projection rows", torch.float32, 2)
+    _check(q_out, "queries", torch.float32, 3)
+    n = proj.shape[0]
+    if q_out.shape != (n, n_heads, kd) or proj.shape[1] < n_heads * kd + n_kv * (kd + vd):
+        raise KernelError("qk_prep: sizes disagree")
+    if n_kv and (cache.head_dim != kd or cache.v_dim != vd or cache.n_kv_heads != n_kv):
+        raise KernelError("qk_prep: the cache does not fit the keys and values")
+    mixers().call("hos_qk_prep", _ptr(proj), proj.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(freq),
+                  int(rot_dims), float(magnitude), _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.seq_slot),
+                  _ptr(q_out), _ptr(cache.k_pages) if n_kv else None, _ptr(cache.v_pages) if n_kv else None,
+                  dtype_code(cache.k_pages.dtype), _ptr(cache.page_table), cache.table_stride, cache.ring_pages, n,
+                  int(n_heads), int(n_kv), int(kd), int(vd), _stream())
+
+
+def gated_attn(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+               gate_col: int, step, out: torch.Tensor, scale: float, chunk: int, window: int, n_splits: int = 1) -> None:
+    """q: float32 [N, H, kd]; keys and values from the paged cache; out: [N, H * vd].  gate: float32 rows whose column
+    gate_col + h is head h's gate logit."""
+    _check(q, "queries", torch.float32, 3)
+    n, heads, kd = q.shape
+    vd = cache.v_dim
+    if out.shape != (n, heads * vd) or kd != cache.head_dim:
+        raise KernelError("gated_attn: sizes disagree")
+    part_acc = part_ml = None
+    if n_splits > 1:
+        part_acc = torch.empty((n, heads, n_splits, vd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    mixers().call("hos_gated_attn", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), dtype_code(cache.k_pages.dtype),
+                  _ptr(cache.page_table), cache.table_stride, cache.ring_pages, _ptr(sink),
+                  ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None,
+                  gate.shape[1] if gate is not None else 0, _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.seq_slot),
+                  _ptr(out), dtype_code(out.dtype), _ptr(part_acc), _ptr(part_ml), int(n_splits), n, heads,
+                  cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), _stream())
+
+
+def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_load: bool, g: torch.Tensor,
+               per_token_g: bool, beta: Optional[torch.Tensor], state: torch.Tensor, step, out: torch.Tensor,
+               heads: int, key_heads: int, dim: int, vdim: int) -> None:
+    """The matrix-state recurrence over the step's sequences.  rows: float32 [N, ld] holding q, k (key_heads x dim) and
+    v (heads x vdim) from the given columns on.  g: [heads] constants, or [N, heads] per token; beta ([N, heads]): the
+    delta rule, None: the plain decay rule.  state: [slots, heads, vdim, dim] float32.  out: float32 [N, heads * vdim]."""
+    _check(rows, "recurrence inputs", torch.float32, 2)
+    _check(state, "recurrent state", torch.float32, 4)
+    _check(out, "recurrence output", torch.float32, 2)
+    _check(g, "decays", torch.float32)
+    n, ld = rows.shape
+    if out.shape != (n, heads * vdim) or tuple(state.shape[1:]) != (heads, vdim, dim):
+        raise KernelError("state_scan: sizes disagree")
+    base = rows.data_ptr()
+    mixers().call("hos_state_scan", ctypes.c_void_p(base + 4 * q_col), ctypes.c_void_p(base + 4 * k_col),
+                  ctypes.c_void_p(base + 4 * v_col), ld, 1 if silu_on_load else 0, _ptr(g), heads if per_token_g else 0,
+                  _ptr(beta), heads if beta is not None else 0, _ptr(state), _ptr(step.token_pos), _ptr(step.token_seq),
+                  _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out), int(step.n_seqs), int(heads), int(key_heads),
+                  int(dim), int(vdim), _stream())
+
+
+def conv_prep(raw: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+              step, act: torch.Tensor, beta: torch.Tensor, g: torch.Tensor, heads: int, key_heads: int, dim: int,
+              vdim: int) -> None:
+    """raw: float32 [N, ld] = [q | k | v | b | a | ...] projections; conv_w: [C, taps]; conv_state: [slots, taps - 1, C]."""
+    _check(raw, "projection rows", torch.float32, 2)
+    _check(conv_w, "convolution weights", torch.float32, 2)
+    n, c = raw.shape[0], 2 * key_heads * dim + heads * vdim
+    taps = conv_w.shape[1]
+    if conv_w.shape[0] != c or raw.shape[1] < c + 2 * heads or act.shape != (n, c) \
+            or tuple(conv_state.shape[1:]) != (max(taps - 1, 0), c):
+        raise KernelError("conv_prep: sizes disagree")
+    mixers().call("hos_conv_prep", _ptr(raw), raw.shape[1], _ptr(conv_w), taps, _ptr(conv_state), _ptr(a_log), _ptr(dt_bias),
+                  _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(act),
+                  _ptr(beta), _ptr(g), n, int(heads), int(key_heads), int(dim), int(vdim), _stream())
+
+
+def conv_keep(raw: torch.Tensor, taps: int, conv_state: torch.Tensor, step, channels: int) -> None:
+    mixers().call("hos_conv_keep", _ptr(raw), raw.shape[1], int(taps), _ptr(conv_state), _ptr(step.token_pos),
+                  _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot), int(step.n_seqs), int(channels),
+                  _stream())

@@ -47,6 +47,7 @@ class KVNeed:
     window: Optional[int]            # None: all keys; an int: the last `window` keys
     keys_only: bool = False          # True: one array per entry instead of two (a mixer whose values are a part
                                      # of what it keeps as keys, e.g. a shared latent row per position)
+    v_head_dim: Optional[int] = None # values of another size than the keys (None: head_dim)
 
 
 @dataclass(frozen=True)

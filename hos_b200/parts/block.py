@@ -9,6 +9,9 @@ sums are 32-bit.
 "parallel": both branches read a norm (each its own weight) of the SAME x, and their sum is scaled,
     x += mult * (mixer(pre_mixer(x)) + ffn(pre_ffn(x)))
     (`mult`: the arrangement's own constant, LayerSpec.params["residual_mult"], default 1).
+"postnorm": the norm comes after the sum, and the branches read the residual stream itself,
+    x <- post_mixer(alpha * x + mixer(x));  x <- post_ffn(alpha * x + ffn(x))
+    (`alpha`: LayerSpec.params["alpha"], default 1; a layer without a feed-forward has the first line only).
 """
 from __future__ import annotations
 
@@ -126,6 +129,55 @@ class ParallelLayer(Layer):
         return next_norm.forward(x) if next_norm is not None else None
 
 
+class PostNormLayer(Layer):
+    """x <- norm(alpha * x + branch(x)) for the mixer and then for the feed-forward.  The sum, the norm and the copy of
+    the new x that the next branch's products read (or the model's last norm of it) are one kernel; x and the sums
+    are 32-bit."""
+    norm_roles = ("post_mixer",)
+    chains = True
+
+    def __init__(self, spec: LayerSpec, rt: Runtime):
+        super().__init__(spec, rt)
+        from .feedforward import NoFeedForward
+        from .norm import RMSNorm, RowsAsGiven
+        self.has_ffn = not isinstance(self.feed_forward, NoFeedForward)
+        roles = ("post_mixer", "post_ffn") if self.has_ffn else ("post_mixer",)
+        for r in roles:
+            if not isinstance(self.norms.get(r), RMSNorm) or self.norms[r].add_one:
+                raise SpecError(f"arch spec error: the postnorm arrangement takes a plain RMS norm as {r}")
+        self.alpha = float(spec.params.get("alpha", 1.0))
+        self._entry = RowsAsGiven(rt)
+
+    def entry_norm(self):
+        return self._entry
+
+    def _sum_norm(self, y, x, norm, nxt):
+        from .norm import RMSNorm, RowsAsGiven
+        if isinstance(nxt, RowsAsGiven):
+            if self.rt.is_fp32:
+                ops.scale_add_norm(y, self.alpha, x, norm.weight, norm.eps)
+                return x
+            h = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+            ops.scale_add_norm(y, self.alpha, x, norm.weight, norm.eps, h)
+            return h
+        if isinstance(nxt, RMSNorm) and not nxt.add_one:
+            h = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+            ops.scale_add_norm(y, self.alpha, x, norm.weight, norm.eps, h, nxt.weight, nxt.eps)
+            return h
+        ops.scale_add_norm(y, self.alpha, x, norm.weight, norm.eps)
+        return nxt.forward(x) if nxt is not None else None
+
+    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore, h_in=None, next_norm=None):
+        h = h_in if h_in is not None else self._entry.forward(x)
+        a = self._branch(self.mixer, True, h, step, store)
+        if not self.has_ffn:
+            return self._sum_norm(a, x, self.norms["post_mixer"], next_norm)
+        h = self._sum_norm(a, x, self.norms["post_mixer"], self._entry)
+        f = self._branch(self.feed_forward, True, h, step)
+        return self._sum_norm(f, x, self.norms["post_ffn"], next_norm)
+
+
 register_part("arrangement", "sandwich", SandwichLayer)
+register_part("arrangement", "postnorm", PostNormLayer)
 register_part("arrangement", "parallel", ParallelLayer)
 register_part("arrangement", "prenorm", PreNormLayer)

@@ -1,0 +1,147 @@
+"""Softmax attention with grouped queries whose pieces are all options: keys of `dim` and values of `vdim`
+numbers per head; biases on the q, k, v projections; an RMS norm of every query and key head (a weight of
+`dim` numbers shared by the heads, before the rotation); a rotary position part on the first numbers of a
+head; scores (q . k) * scale; a mask of chunks (position i sees j <= i with floor(j / C) = floor(i / C),
+counted from the sequence's position 0) or of a window (the last W keys), or plain causal; a sink (a learned
+number per head whose exponential joins the softmax's denominator, without a key or a value); a gate per head
+(the head's output times the logistic function of a projection of the mixer's input); the output projection.
+
+A call that reads another call's cache (`shares_kv`) has no key or value tensors: it projects its own queries
+and gate and attends over the other call's keys and values as the cache holds them.
+
+Every row stores its key and value first and then attends over the cache, whether its sequence starts in this
+step or goes on: a position's result does not depend on how a prompt was cut.  The projections come out of
+one product in 32-bit; norms, angles, scores, weights and the weighted sums are 32-bit; the cache holds keys
+and values in the products' type.
+"""
+from __future__ import annotations
+
+from typing import List, Mapping, Optional
+
+import torch
+
+from .. import ops
+from ..errors import KernelError, SpecError
+from ..registry import part_impl, register_part
+from . import linear
+from .base import CallStore, KVNeed, Mixer, StepInfo, WeightSpec
+
+SPLIT_MIN_KEYS = 256        # rows that see fewer keys are never cut into shares
+
+
+class GatedSoftmaxAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = spec.params
+        self.width = int(p["width"])
+        self.n_heads, self.n_kv_heads = int(p["n_heads"]), int(p["n_kv_heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.scale = float(p["scale"])
+        self.eps = float(p.get("eps", 1e-6))
+        self.chunk: Optional[int] = p.get("chunk")
+        self.window: Optional[int] = p.get("window")
+        self.has_bias, self.qk_norm = bool(p.get("bias", False)), bool(p.get("qk_norm", False))
+        self.has_sink, self.head_gate = bool(p.get("sink", False)), bool(p.get("head_gate", False))
+        self.shares_kv = bool(p.get("shares_kv", False))
+        if min(self.n_heads, self.n_kv_heads, self.dim, self.vdim) <= 0 or self.n_heads % self.n_kv_heads != 0:
+            raise SpecError(f"arch spec error: {self.n_heads} heads of {self.dim}/{self.vdim} numbers over "
+                            f"{self.n_kv_heads} kv heads")
+        for name, v in (("chunk", self.chunk), ("window", self.window)):
+            if v is not None and int(v) <= 0:
+                raise SpecError(f"arch spec error: the attention's {name} must be positive")
+        pos_spec = p.get("position")
+        self.position = part_impl("position", pos_spec.kind)(pos_spec, rt) if pos_spec else None
+        self.q_cols = self.n_heads * self.dim
+        self.kv_cols = 0 if self.shares_kv else self.n_kv_heads * (self.dim + self.vdim)
+        self.gate_col = self.q_cols + self.kv_cols
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w = self.spec.weights
+        out = [WeightSpec(w["q"], (self.q_cols, self.width), "matrix", 0.02),
+               WeightSpec(w["o"], (self.width, self.n_heads * self.vdim), "matrix", 0.02)]
+        roles = [("q", self.q_cols)]
+        if not self.shares_kv:
+            out += [WeightSpec(w["k"], (self.n_kv_heads * self.dim, self.width), "matrix", 0.02),
+                    WeightSpec(w["v"], (self.n_kv_heads * self.vdim, self.width), "matrix", 0.02)]
+            roles += [("k", self.n_kv_heads * self.dim), ("v", self.n_kv_heads * self.vdim)]
+        if self.has_bias:
+            out += [WeightSpec(w[r + "_bias"], (n,), "vector", 0.1) for r, n in roles]
+        if self.qk_norm:
+            out += [WeightSpec(w[r + "_norm"], (self.dim,), "vector", 0.1) for r, _ in roles if r != "v"]
+        if self.has_sink:
+            out.append(WeightSpec(w["sink"], (self.n_heads,), "vector", 0.5))
+        if self.head_gate:
+            out.append(WeightSpec(w["gate"], (self.n_heads, self.width), "matrix", 0.05))
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        w = self.spec.weights
+        roles = ["q"] if self.shares_kv else ["q", "k", "v"]
+        mats = [self._matrix(tensors[w[r]]) for r in roles]
+        if self.head_gate:
+            mats.append(self._matrix(tensors[w["gate"]]))
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.float() for m in mats]
+        self.w_in = torch.cat(mats, dim=0).contiguous()          # one product: q | k | v | gate logits
+        self.bias = None
+        if self.has_bias:
+            parts = [self._vector32(tensors[w[r + "_bias"]]) for r in roles]
+            if self.head_gate:
+                parts.append(torch.zeros(self.n_heads, dtype=torch.float32, device=parts[0].device))
+            self.bias = torch.cat(parts).contiguous()
+        self.q_norm = self._vector32(tensors[w["q_norm"]]) if self.qk_norm else None
+        self.k_norm = self._vector32(tensors[w["k_norm"]]) if self.qk_norm and not self.shares_kv else None
+        self.sink = self._vector32(tensors[w["sink"]]) if self.has_sink else None
+        self.w_o = self._matrix(tensors[w["o"]])
+
+    def kv_need(self) -> KVNeed:
+        # every position is kept: rows attend over the cache in the step that stores them too, and a prompt may
+        # be longer than any ring
+        return KVNeed(self.n_kv_heads, self.dim, None, False, self.vdim if self.vdim != self.dim else None)
+
+    def keys_seen(self, longest: int) -> int:
+        n = longest
+        if self.chunk:
+            n = min(n, int(self.chunk))
+        if self.window:
+            n = min(n, int(self.window))
+        return max(1, n)
+
+    def n_splits(self, n_rows: int, longest: int) -> int:
+        """Into how many shares a row's keys are cut: only where the rows alone leave most of the GPU idle."""
+        keys = self.keys_seen(longest)
+        warps = n_rows * self.n_heads
+        room = 8 * ops.sm_count()
+        if keys < SPLIT_MIN_KEYS or warps >= room:
+            return 1
+        return max(1, min(room // warps, keys // 128, 64))
+
+    def forward(self, h, step: StepInfo, store: CallStore):
+        return self._run(h, step, store, False)
+
+    def forward_partial(self, h, step: StepInfo, store: CallStore):
+        return self._run(h, step, store, True)
+
+    def _run(self, h: torch.Tensor, step: StepInfo, store: CallStore, partial_ok: bool) -> torch.Tensor:
+        cache = store.kv
+        if cache is None:
+            raise KernelError("attention needs a cache view")
+        if store.owns_kv == self.shares_kv:
+            raise KernelError("attention: the call's cache and the mixer's tensors do not fit (a mixer without key and "
+                              "value tensors reads another call's cache, and only such a mixer does)")
+        n = h.shape[0]
+        proj = linear.matmul(h, self.w_in, out_dtype=torch.float32)
+        q = torch.empty((n, self.n_heads, self.dim), dtype=torch.float32, device=h.device)
+        freq, rot_dims, _ = self.position.kernel_args() if self.position else (None, 0, 0)
+        ops.qk_prep(proj, self.bias, self.q_norm, self.k_norm, self.eps, freq, rot_dims,
+                    getattr(self.position, "magnitude", 1.0), step, q, cache, self.n_heads,
+                    0 if self.shares_kv else self.n_kv_heads, self.dim, self.vdim)
+        att = torch.empty((n, self.n_heads * self.vdim), dtype=h.dtype, device=h.device)
+        ops.gated_attn(q, cache, self.sink, proj if self.head_gate else None, self.gate_col, step, att, self.scale,
+                       self.chunk or 0, self.window or 0, self.n_splits(n, step.max_len_after))
+        return linear.matmul_or_partials(att, self.w_o) if partial_ok else linear.matmul(att, self.w_o)
+
+
+register_part("mixer", "gated_softmax_attention", GatedSoftmaxAttention)

@@ -67,3 +67,18 @@ class NormPair:
         ops.scaled_add_norms(None, None, 0.0, x, self.first.weight, self.first.eps, h1,
                              self.second.weight, self.second.eps, h2)
         return h1, h2
+
+
+class RowsAsGiven:
+    """Stands where an arrangement expects the norm that a layer's first branch reads, for layers whose branches
+    read the residual stream itself: `forward(x)` is x in the products' type (x itself in the 32-bit path)."""
+
+    def __init__(self, rt):
+        self.rt = rt
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.rt.is_fp32:
+            return x
+        h = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        ops.cast_rows(x, h)
+        return h
