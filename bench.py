@@ -12,7 +12,7 @@ back to the host, where the loop reads them one step late.  `prefill` is one pro
 step must read (every weight once, and the cache of the live sequences) to its time.
 `points` holds decoding at batch 1 and 64.  One JSON line is printed.
 
-`--design satapel` is another measurement (not the line above): prompt and decode throughput of the Satapel design at
+`--design satapel` (or `vagonex`) is another measurement (not the line above): prompt and decode throughput of that design at
 a few sizes beside Gemma-2 at equal size, and each of the design's kernels against its roofline; one JSON line per size.
 
 Random weights are made on the device; the cache of the decode measurements is filled with
@@ -344,12 +344,81 @@ def satapel_kernel_work(z, tokens, batch, ctx):
     }
 
 
+# ---- --design vagonex: the Vagonex design beside Gemma-2 at equal size -----------------------------------
+# Layers in the order (decay, delta, attention, delta) x blocks; attention with chunks; a dense gated feed-forward.
+# Gemma-2 "at equal size": the same width, layer count, vocabulary, heads, head size and intermediate size, its
+# window as long as the chunks.
+VAGONEX_SIZES = {
+    "s": dict(width=1024, vocab=32000, blocks=2, heads=8, kv_heads=2, dim=128, vdim=128, chunk=1024, ff=4096,
+              state_heads=8, state_kv=4, state_dim=128, state_vdim=128, conv=4),
+    "m": dict(width=2048, vocab=32000, blocks=2, heads=16, kv_heads=4, dim=128, vdim=128, chunk=2048, ff=8192,
+              state_heads=16, state_kv=8, state_dim=128, state_vdim=128, conv=4),
+    "l": dict(width=4096, vocab=64000, blocks=1, heads=32, kv_heads=8, dim=128, vdim=128, chunk=2048, ff=14336,
+              state_heads=32, state_kv=16, state_dim=128, state_vdim=128, conv=4),
+}
+
+
+def vagonex_raw(z):
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                     "scale": z["dim"] ** -0.5, "mask": {"size": z["chunk"]},
+                     "rot": {"base": 10000.0, "dims": z["dim"] // 2,
+                             "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    dec = {"type": "lightning", "mlp": mlp,
+           "mixer": {"heads": z["state_heads"], "dim": z["state_dim"], "vdim": z["state_vdim"],
+                     "decay": [1.0 - 2.0 ** -(3 + 5 * i / max(1, z["state_heads"] - 1)) for i in range(z["state_heads"])]}}
+    dlt = {"type": "delta", "mlp": mlp,
+           "mixer": {"heads": z["state_heads"], "kv_heads": z["state_kv"], "dim": z["state_dim"], "vdim": z["state_vdim"],
+                     "conv": z["conv"]}}
+    return {"architecture": "Vagonex", "vocab": z["vocab"], "width": z["width"], "postln_alpha": 2.0, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(z["width"]) ** 0.5}, "layers": [dec, dlt, att, dlt] * z["blocks"]}
+
+
+def gemma_raw_like_vagonex(z):
+    return dict(architectures=["Gemma2ForCausalLM"], model_type="gemma2", num_hidden_layers=4 * z["blocks"],
+                hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                head_dim=z["dim"], intermediate_size=z["ff"], vocab_size=z["vocab"], rope_theta=10000.0,
+                sliding_window=z["chunk"], max_position_embeddings=8192, query_pre_attn_scalar=z["dim"],
+                attn_logit_softcapping=50.0, final_logit_softcapping=30.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
+
+
+def vagonex_kernel_work(z, tokens, batch, ctx):
+    """Per launch of each of the design's own kernels: (bytes that must move, FLOPs of the mathematics) for a prompt of
+    `tokens` tokens and for a decode step of `batch` sequences at length `ctx` (bfloat16 cache, 32-bit state and rows)."""
+    H, G, kd, vd, C = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["chunk"]
+    pairs = sum(p % C + 1 for p in range(tokens))
+    keys = (ctx - 1) % C + 1
+    sh, sk, sd, sv = z["state_heads"], z["state_kv"], z["state_dim"], z["state_vdim"]
+    cols = 2 * sk * sd + sh * sv                      # the delta rule's q, k, v columns (the decay rule has sh key heads)
+    width = z["width"]
+
+    def scan(n, seqs):        # rows in and out, the state in and out; S update and read-out: 4 (decay) to 7 (delta) per cell
+        return n * (cols + sh * sv) * 4 + seqs * sh * sd * sv * 4 * 2, 7.0 * n * sh * sd * sv
+    return {
+        "hos_gated_attn": {"prefill": (tokens * G * (kd + vd) * 2 + tokens * H * (kd * 4 + vd * 2), 2.0 * pairs * H * (kd + vd)),
+                           "decode": (batch * keys * G * (kd + vd) * 2, 2.0 * batch * keys * H * (kd + vd))},
+        "hos_state_scan": {"prefill": scan(tokens, 1), "decode": scan(batch, batch)},
+        "hos_qk_prep": {"prefill": (tokens * (H * kd * 8 + G * (kd + vd) * 6), 0.0),
+                        "decode": (batch * (H * kd * 8 + G * (kd + vd) * 6), 0.0)},
+        "hos_conv_prep": {"prefill": (tokens * cols * 8, 0.0), "decode": (batch * cols * (8 + 4 * (z["conv"] - 1)), 0.0)},
+        "hos_group_norm_gate": {"prefill": (tokens * sh * sv * 10, 0.0), "decode": (batch * sh * sv * 10, 0.0)},
+        "hos_scale_add_norm": {"prefill": (tokens * width * 12, 0.0), "decode": (batch * width * 12, 0.0)},
+    }
+
+
+DESIGNS = {"satapel": lambda: (SATAPEL_SIZES, satapel_raw, gemma_raw_like, satapel_kernel_work, ("hos_wkv_scan",)),
+           "vagonex": lambda: (VAGONEX_SIZES, vagonex_raw, gemma_raw_like_vagonex, vagonex_kernel_work,
+                               ("hos_state_scan", "hos_gated_attn"))}
+
+
 def run_design_comparison(args) -> int:
     """Prompt and decode throughput of Satapel beside Gemma-2 at equal size, and where each of the design's own
     kernels stands against its roofline: the larger of (bytes over the measured copy rate) and (the FLOPs of the
     mathematics over the measured bfloat16 tensor rate; for the recurrence, which is 32-bit FMA work, over the FMA
     pipes' rate).  The attention kernel issues twice its mathematics' FLOPs (two bfloat16 terms per 32-bit operand);
-    the fraction counts the mathematics only.  One JSON line per size."""
+    the fraction counts the mathematics only.  The Vagonex attention and scans are 32-bit FMA work and are held to the
+    FMA pipes' rate.  One JSON line per size."""
     import random
     import torch
     from hos_b200 import Engine, ops
@@ -357,11 +426,12 @@ def run_design_comparison(args) -> int:
     pk, pk_src = peaks()
     rng = random.Random(0)
     tokens, ctx = args.prefill_tokens, args.ctx if args.ctx != 8192 else 2048
+    sizes, raw_of, gemma_of, work_of, fma_kernels = DESIGNS[args.design]()
     for name in args.sizes.split(","):
-        z = SATAPEL_SIZES[name]
-        line = {"design": "satapel", "size": name, "sizes": z, "prompt_tokens": tokens, "decode_ctx": ctx, "peaks": pk_src,
+        z = sizes[name]
+        line = {"design": args.design, "size": name, "sizes": z, "prompt_tokens": tokens, "decode_ctx": ctx, "peaks": pk_src,
                 "dtype": "bf16", "data": "synthetic (random weights)"}
-        for which, raw in (("satapel", satapel_raw(z)), ("gemma2_equal_size", gemma_raw_like(z))):
+        for which, raw in ((args.design, raw_of(z)), ("gemma2_equal_size", gemma_of(z))):
             cfg = config_from_dict(raw)
             batches = [int(b) for b in args.batches.split(",")]
             eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_batch=max(batches),
@@ -404,13 +474,13 @@ def run_design_comparison(args) -> int:
                 ops.time_calls(False)
                 for s in slots:
                     r.release(s)
-                work = satapel_kernel_work(z, tokens, b, ctx) if which == "satapel" else {}
+                work = work_of(z, tokens, b, ctx) if which == args.design else {}
                 rows = {}
                 for fn, (n, ms) in sorted(times.items(), key=lambda kv: -kv[1][1]):
                     row = {"calls": n, "ms": round(ms, 4)}
                     if fn in work:
                         by, fl = work[fn][phase]
-                        tensor = fn != "hos_wkv_scan"        # bfloat16 products and the attention: tensor cores
+                        tensor = fn not in fma_kernels       # bfloat16 products and the latent attention: tensor cores
                         t_mem = by / (pk["hbm_gbs"] * 1e9)
                         t_fl = fl / ((pk["bf16_tflops"] if tensor else FP32_TFLOPS) * 1e12)
                         row["roofline_us_per_call"] = round(max(t_mem, t_fl) * 1e6, 2)
@@ -448,7 +518,7 @@ def main() -> int:
                          "instead of all at its end (not the driver's line: how a batch of unequal lengths decodes)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the timed prompt (default: the contract's 2,048)")
-    ap.add_argument("--design", default=None, choices=["satapel"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="not the driver's line: prompt and decode throughput of this design beside Gemma-2 at equal "
                          "size, with its kernels against their rooflines (--sizes, --batches, --ctx, --prefill-tokens)")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of the sizes s, m, l")

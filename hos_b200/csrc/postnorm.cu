@@ -89,6 +89,8 @@ group_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w,
 
 using namespace hos;
 
+extern "C" const char* hos_last_error() { return error_buffer(); }
+
 // y: [N][D] of y_dtype, or n_parts > 1 planes of float32 partial sums.  h (of h_dtype) may be null; with w_next
 // null it is x itself in that type, else the next norm of x.
 extern "C" int hos_scale_add_norm(const void* y, int y_dtype, int n_parts, float alpha, float* x, const float* w, float eps,

@@ -251,13 +251,16 @@ extern "C" int hos_state_scan(const float* q, const float* k, const float* v, lo
     const size_t smem = (size_t)(2 * kScanChunk * dpad + 2 * kScanChunk * CC + 2 * kScanChunk) * sizeof(float);
     const dim3 grid(n_seqs, H, (vdim + CC - 1) / CC);
     const bool delta = beta != nullptr;
+    if (smem > 200 * 1024) HOS_REFUSE("state_scan: heads of %d x %d do not fit a block's shared memory", dim, vdim);
 #define HOS_SCAN(DRv, DL)                                                                                            \
+    if (smem > 48 * 1024)                                                                                            \
+        cudaFuncSetAttribute(state_scan_kernel<DRv, DL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     launch_pdl(state_scan_kernel<DRv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, silu_on_load, g, g_ld, beta, \
                beta_ld, state, token_pos, token_seq, cu_seqlens, seq_slot, out, H, Gk, dim, vdim, R, CC)
 #define HOS_SCAN_D(DRv)                                                                                              \
     do {                                                                                                             \
-        if (delta) HOS_SCAN(DRv, true);                                                                              \
-        else HOS_SCAN(DRv, false);                                                                                   \
+        if (delta) { HOS_SCAN(DRv, true); }                                                                          \
+        else { HOS_SCAN(DRv, false); }                                                                                 \
     } while (0)
     if (DR == 4) HOS_SCAN_D(4);
     else if (DR == 8) HOS_SCAN_D(8);
