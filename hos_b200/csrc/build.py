@@ -50,7 +50,7 @@ _STATIC_LIBS: Dict[str, Tuple[List[str], List[str]]] = {
     "gemm_tc": (["gemm_tc.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "blocks": (["embed_pair.cu", "latent_attention.cu", "wkv.cu", "moe.cu"], []),
-    "mixers": (["postnorm.cu", "gated_attention.cu", "state_scan.cu"], []),
+    "mixers": (["postnorm.cu", "gated_attention.cu", "gated_attention_mma.cu", "state_scan.cu"], []),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

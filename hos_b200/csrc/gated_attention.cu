@@ -7,8 +7,9 @@
 //   the heads, its first rot_dims numbers are rotated as neighbouring pairs (2i, 2i+1) by the angle
 //   position * freq[i], cosine and sine times `magnitude`; queries are written as 32-bit rows, keys and values
 //   (in the cache's type) to their places in the paged cache.
-// gated_attn: one warp per (token, query head, share of the keys).  A lane takes a key: 32 scores at a time, then
-//   the lanes turn to the value columns.  Keys j of position i: j <= i and, with chunks of size C,
+// gated_attn: one warp per (token, up to 8 query heads that share a kv head, share of the keys).  A lane takes a
+//   key: 32 scores per head at a time, then the lanes turn to the value columns; a key or value row is read once
+//   for all of the warp's heads.  Keys j of position i: j <= i and, with chunks of size C,
 //   floor(j / C) = floor(i / C); with a window W, j > i - W.  The denominator also holds exp(sink[head]).
 //   The head's output is multiplied by the logistic function of its gate logit.  With more than one share the
 //   partial (maximum, sum, weighted values) go to a workspace and attn_merge adds them.
@@ -129,7 +130,7 @@ __device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
     }
 }
 
-template <typename TC, int VPL>
+template <typename TC, int VPL, int QH>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __restrict__ sink, const float* __restrict__ gate,
                   long long gate_stride, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
@@ -139,23 +140,28 @@ gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __re
     pdl_enter();
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long item = (long long)blockIdx.x * kAttnWarps + warp;
-    if (item >= (long long)n_tokens * H * n_splits) return;
+    const int groups = H / QH;                       // QH query heads that share a kv head go together: its keys and
+    const long long item = (long long)blockIdx.x * kAttnWarps + warp;      // values are read once for all of them
+    if (item >= (long long)n_tokens * groups * n_splits) return;
     const int split = (int)(item % n_splits);
-    const int h = (int)((item / n_splits) % H), n = (int)(item / ((long long)n_splits * H));
+    const int h0 = (int)((item / n_splits) % groups) * QH, n = (int)(item / ((long long)n_splits * groups));
     const int seq = token_seq[n];
-    const size_t orow = ((size_t)n * H + h) * vd;
     if (seq < 0) {
-        if (n_splits == 1)
-            for (int d = lane; d < vd; d += 32) {
-                if (out_bf16) ((bf16*)out)[orow + d] = from_float<bf16>(0.f);
-                else ((float*)out)[orow + d] = 0.f;
-            }
-        else if (lane < 2) part_ml[(((size_t)n * H + h) * n_splits + split) * 2 + lane] = lane == 0 ? -INFINITY : 0.f;
+#pragma unroll
+        for (int hh = 0; hh < QH; ++hh) {
+            const size_t orow = ((size_t)n * H + h0 + hh) * vd;
+            if (n_splits == 1)
+                for (int d = lane; d < vd; d += 32) {
+                    if (out_bf16) ((bf16*)out)[orow + d] = from_float<bf16>(0.f);
+                    else ((float*)out)[orow + d] = 0.f;
+                }
+            else if (lane < 2)
+                part_ml[(((size_t)n * H + h0 + hh) * n_splits + split) * 2 + lane] = lane == 0 ? -INFINITY : 0.f;
+        }
         return;
     }
     const int pos = token_pos[n];
-    const int g = h / (H / G);
+    const int g = h0 / (H / G);
     int lo = 0;
     if (chunk > 0) lo = pos / chunk * chunk;
     if (window > 0) lo = max(lo, pos + 1 - window);
@@ -166,84 +172,113 @@ gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __re
         hi = min(hi, a + per * 32);
         lo = a;
     }
-    float* qs = qs_all + warp * kd;
-    const float* qp = q + ((size_t)n * H + h) * kd;
-    for (int d = lane; d < kd; d += 32) qs[d] = qp[d];
+    float* qs = qs_all + warp * QH * kd;
+    const float* qp = q + ((size_t)n * H + h0) * kd;
+    for (int d = lane; d < QH * kd; d += 32) qs[d] = qp[d];
     __syncwarp();
     const int slot = seq_slot[seq];
     const int* table = cache.page_table + (size_t)slot * cache.table_stride;
 
     // the sink takes part once: in the first share
     const bool with_sink = sink != nullptr && split == 0;
-    float m = with_sink ? sink[h] : -INFINITY;
-    float l = with_sink ? 1.f : 0.f;
-    float acc[VPL];
+    float m[QH], l[QH], acc[QH][VPL];
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+    for (int hh = 0; hh < QH; ++hh) {
+        m[hh] = with_sink ? sink[h0 + hh] : -INFINITY;
+        l[hh] = with_sink ? 1.f : 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[hh][i] = 0.f;
+    }
     const bool vec = (kd & 7) == 0;
 
     for (int t0 = lo; t0 < hi; t0 += 32) {
         const int t = t0 + lane;
-        float s = -INFINITY;
+        float s[QH];
+#pragma unroll
+        for (int hh = 0; hh < QH; ++hh) s[hh] = -INFINITY;
         int my_page = 0;
         if (t < hi) {
             my_page = table[table_entry(cache, t / kPageTokens)];
             const int r = t % kPageTokens;
             const TC* kp = (const TC*)cache.k_pages + ((size_t)my_page * G + g) * (size_t)kPageTokens * kd;
-            float dot = 0.f;
+            float dot[QH];
+#pragma unroll
+            for (int hh = 0; hh < QH; ++hh) dot[hh] = 0.f;
             if (vec) {
                 for (int c = 0; c < kd; c += 8) {
                     float f[8];
                     load8(kp + kv_elem_offset(r, c, kd), f);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) dot = fmaf(qs[c + e], f[e], dot);
+                    for (int hh = 0; hh < QH; ++hh)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) dot[hh] = fmaf(qs[hh * kd + c + e], f[e], dot[hh]);
                 }
             } else {
-                for (int d = 0; d < kd; ++d) dot = fmaf(qs[d], to_float(kp[kv_elem_offset(r, d, kd)]), dot);
-            }
-            s = dot * scale;
-        }
-        const float m_new = fmaxf(m, warp_max(s));
-        const float corr = expf(m - m_new);          // m_new is finite here: the block holds one key at least
-        const float p = t < hi ? expf(s - m_new) : 0.f;
-        l = l * corr + warp_sum(p);
+                for (int d = 0; d < kd; ++d) {
+                    const float kv = to_float(kp[kv_elem_offset(r, d, kd)]);
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) acc[i] *= corr;
-        m = m_new;
+                    for (int hh = 0; hh < QH; ++hh) dot[hh] = fmaf(qs[hh * kd + d], kv, dot[hh]);
+                }
+            }
+#pragma unroll
+            for (int hh = 0; hh < QH; ++hh) s[hh] = dot[hh] * scale;
+        }
+        float p[QH];
+#pragma unroll
+        for (int hh = 0; hh < QH; ++hh) {
+            const float m_new = fmaxf(m[hh], warp_max(s[hh]));
+            const float corr = expf(m[hh] - m_new);          // m_new is finite here: the block holds one key at least
+            p[hh] = t < hi ? expf(s[hh] - m_new) : 0.f;
+            l[hh] = l[hh] * corr + warp_sum(p[hh]);
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) acc[hh][i] *= corr;
+            m[hh] = m_new;
+        }
         const int cnt = min(32, hi - t0);
         for (int j = 0; j < cnt; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, p, j);
             const int pg = __shfl_sync(0xffffffffu, my_page, j);
             const int r = (t0 + j) % kPageTokens;
             const TC* vp = (const TC*)cache.v_pages + ((size_t)pg * G + g) * (size_t)kPageTokens * vd;
+            float vv[VPL];
 #pragma unroll
             for (int i = 0; i < VPL; ++i) {
                 const int d = lane + 32 * i;
-                if (d < vd) acc[i] = fmaf(pj, to_float(vp[kv_elem_offset(r, d, vd)]), acc[i]);
+                vv[i] = d < vd ? to_float(vp[kv_elem_offset(r, d, vd)]) : 0.f;
+            }
+#pragma unroll
+            for (int hh = 0; hh < QH; ++hh) {
+                const float pj = __shfl_sync(0xffffffffu, p[hh], j);
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) acc[hh][i] = fmaf(pj, vv[i], acc[hh][i]);
             }
         }
     }
-    if (n_splits > 1) {
-        const size_t pi = ((size_t)n * H + h) * n_splits + split;
-        if (lane == 0) {
-            part_ml[pi * 2] = m;
-            part_ml[pi * 2 + 1] = l;
+#pragma unroll
+    for (int hh = 0; hh < QH; ++hh) {
+        const int h = h0 + hh;
+        const size_t orow = ((size_t)n * H + h) * vd;
+        if (n_splits > 1) {
+            const size_t pi = ((size_t)n * H + h) * n_splits + split;
+            if (lane == 0) {
+                part_ml[pi * 2] = m[hh];
+                part_ml[pi * 2 + 1] = l[hh];
+            }
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < vd) part_acc[pi * vd + d] = acc[hh][i];
+            }
+            continue;
         }
+        float f = l[hh] > 0.f ? 1.f / l[hh] : 0.f;
+        if (gate != nullptr) f *= 1.f / (1.f + expf(-gate[(size_t)n * gate_stride + h]));
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             const int d = lane + 32 * i;
-            if (d < vd) part_acc[pi * vd + d] = acc[i];
-        }
-        return;
-    }
-    float f = l > 0.f ? 1.f / l : 0.f;
-    if (gate != nullptr) f *= 1.f / (1.f + expf(-gate[(size_t)n * gate_stride + h]));
-#pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-        const int d = lane + 32 * i;
-        if (d < vd) {
-            if (out_bf16) ((bf16*)out)[orow + d] = from_float<bf16>(acc[i] * f);
-            else ((float*)out)[orow + d] = acc[i] * f;
+            if (d < vd) {
+                if (out_bf16) ((bf16*)out)[orow + d] = from_float<bf16>(acc[hh][i] * f);
+                else ((float*)out)[orow + d] = acc[hh][i] * f;
+            }
         }
     }
 }
@@ -317,27 +352,43 @@ extern "C" int hos_gated_attn(const float* q, void* k_pages, void* v_pages, int 
     if (vd <= 0 || vd > 32 * kMaxVPL) HOS_REFUSE("gated_attn: value heads of %d numbers are outside 1..%d", vd, 32 * kMaxVPL);
     if (n_splits < 1 || (n_splits > 1 && (part_acc == nullptr || part_ml == nullptr)))
         HOS_REFUSE("gated_attn: %d shares need a workspace", n_splits);
-    const size_t smem = (size_t)kAttnWarps * kd * sizeof(float);
+    // query heads that share a kv head go to one warp, as many as its registers and shared memory take
+    const int vpl = vd <= 32 ? 1 : (vd <= 64 ? 2 : (vd <= 128 ? 4 : (vd <= 256 ? 8 : 16)));
+    int qh = 1;
+    for (int c = 8; c > 1; c >>= 1)
+        if ((H / G) % c == 0 && c * vpl <= 32 && (size_t)kAttnWarps * c * kd * sizeof(float) <= 48 * 1024) {
+            qh = c;
+            break;
+        }
+    const size_t smem = (size_t)kAttnWarps * qh * kd * sizeof(float);
     if (smem > 48 * 1024) HOS_REFUSE("gated_attn: heads of %d numbers do not fit", kd);
     PagedKV2 c{k_pages, v_pages, page_table, table_stride, ring_pages, G, kd, vd};
-    const long long items = (long long)N * H * n_splits;
+    const long long items = (long long)N * (H / qh) * n_splits;
     const unsigned blocks = (unsigned)((items + kAttnWarps - 1) / kAttnWarps);
     const int out_bf16 = out_dtype == kBF16;
-#define HOS_GA(TC, VPL)                                                                                              \
-    launch_pdl(gated_attn_kernel<TC, VPL>, dim3(blocks), dim3(kAttnWarps * 32), smem, stream, q, c, sink, gate,      \
+#define HOS_GA(TC, VPL, QH)                                                                                          \
+    launch_pdl(gated_attn_kernel<TC, VPL, QH>, dim3(blocks), dim3(kAttnWarps * 32), smem, stream, q, c, sink, gate,  \
                gate_stride, token_pos, token_seq, seq_slot, out, out_bf16, part_acc, part_ml, n_splits, N, H, G, kd, vd, \
                scale, chunk, window)
+#define HOS_GA_Q(TC, VPL)                                                                                            \
+    do {                                                                                                             \
+        if (qh == 8) { if constexpr (VPL <= 4) HOS_GA(TC, VPL, 8); }                                                 \
+        else if (qh == 4) { if constexpr (VPL <= 8) HOS_GA(TC, VPL, 4); }                                            \
+        else if (qh == 2) HOS_GA(TC, VPL, 2);                                                                        \
+        else HOS_GA(TC, VPL, 1);                                                                                     \
+    } while (0)
 #define HOS_GA_T(TC)                                                                                                 \
     do {                                                                                                             \
-        if (vd <= 32) HOS_GA(TC, 1);                                                                                 \
-        else if (vd <= 64) HOS_GA(TC, 2);                                                                            \
-        else if (vd <= 128) HOS_GA(TC, 4);                                                                           \
-        else if (vd <= 256) HOS_GA(TC, 8);                                                                           \
-        else HOS_GA(TC, 16);                                                                                         \
+        if (vd <= 32) HOS_GA_Q(TC, 1);                                                                               \
+        else if (vd <= 64) HOS_GA_Q(TC, 2);                                                                          \
+        else if (vd <= 128) HOS_GA_Q(TC, 4);                                                                         \
+        else if (vd <= 256) HOS_GA_Q(TC, 8);                                                                         \
+        else HOS_GA_Q(TC, 16);                                                                                       \
     } while (0)
     if (cache_dtype == kBF16) HOS_GA_T(bf16);
     else HOS_GA_T(float);
 #undef HOS_GA_T
+#undef HOS_GA_Q
 #undef HOS_GA
     int rc = check_launch("gated_attn");
     if (rc != 0 || n_splits == 1) return rc;

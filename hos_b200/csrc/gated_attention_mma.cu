@@ -1,0 +1,246 @@
+// The attention of gated_attention.cu for rows that come many to a sequence (prompts, pieces of prompts), in
+// bfloat16 on the tensor cores, flash style, over the paged cache.
+//
+// One CTA (4 warps) takes 64 consecutive rows of one sequence and one query head; key and value tiles of 64
+// positions are pages of the cache, copied as they lie (the cache's permutation of 16-byte groups is the one the
+// kernel reads with) through a two-stage cp.async pipeline.  Per tile each warp computes S = Q K^T for its 16
+// queries (m16n8k16, 32-bit accumulators: with bfloat16 operands every product is exact, so the scores are 32-bit
+// sums), scales, masks (causal; the chunk's first key; the window's edge), keeps the running maximum and sum in
+// 32-bit and accumulates O += P V with the 32-bit weights P fed as two bfloat16 terms (P = hi + lo, 16 bits of
+// mantissa) so that the weights are not rounded to 8 bits.  The sink starts the running maximum and the sum
+// (exp(sink - max) counts once); the head's gate multiplies the output.  Keys of KD and values of VD numbers,
+// compiled for 64 and 128 each.
+#include "common.cuh"
+#include "kv_layout.cuh"
+#include "mma_utils.cuh"
+
+namespace hos {
+
+constexpr int MQ = 64, MK = 64;       // queries per CTA, keys per tile (a page)
+
+__device__ __forceinline__ void cp16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int KD, int VD>
+__global__ void __launch_bounds__(128)
+gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                      const int* __restrict__ page_table, int table_stride, int ring_pages, const float* __restrict__ sink,
+                      const float* __restrict__ gate, long long gate_stride, const int* __restrict__ cu_seqlens,
+                      const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                      bf16* __restrict__ out, int n_seqs, int H, int G, float scale, int chunk, int window) {
+    pdl_enter();
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [64][KD]
+    bf16* kv_s = q_s + MQ * KD;                                    // stage s: K [64][KD] then V [64][VD]
+    constexpr int kStage = MK * (KD + VD);
+
+    int seq = 0, tile_in_seq = blockIdx.x, row0 = 0, len = 0;
+    for (; seq < n_seqs; ++seq) {
+        row0 = cu_seqlens[seq];
+        len = cu_seqlens[seq + 1] - row0;
+        if (len > 0 && token_seq[row0] < 0) len = 0;               // padding
+        const int nt = (len + MQ - 1) / MQ;
+        if (tile_in_seq < nt) break;
+        tile_in_seq -= nt;
+    }
+    if (seq >= n_seqs) return;
+    const int head = blockIdx.y, kvh = head / (H / G);
+    const int q0 = tile_in_seq * MQ;
+    const int q_rows = min(MQ, len - q0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int p0 = token_pos[row0] + q0;                            // the position of the CTA's first query
+    const int last_q = p0 + q_rows - 1;
+    int first_key = chunk > 0 ? p0 / chunk * chunk : 0;
+    if (window > 0) first_key = max(first_key, p0 + 1 - window);
+    const int kt_lo = first_key / MK, kt_hi = last_q / MK;
+    const int n_kt = kt_hi - kt_lo + 1;
+    const int* table = page_table + (size_t)seq_slot[seq] * table_stride;
+
+    // the queries: 32-bit rows, rounded here to the tensor cores' type; rows beyond the sequence are zeros
+    for (int i = threadIdx.x; i < MQ * (KD / 8); i += 128) {
+        const int r = i / (KD / 8), c = i % (KD / 8);
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (r < q_rows) {
+            const float* src = q + ((size_t)(row0 + q0 + r) * H + head) * KD + c * 8;
+            const float4 a = *(const float4*)src, b = *(const float4*)(src + 4);
+            packed = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+        }
+        *reinterpret_cast<uint4*>(q_s + tile_chunk_offset<KD>(r, c)) = packed;
+    }
+    auto load_kv = [&](int kt, int stage) {
+        const int lp = kt;                                          // a tile is a page
+        const int page = table[ring_pages > 0 ? lp % ring_pages : lp];
+        const bf16* ksrc = k_pages + ((size_t)page * G + kvh) * (size_t)kPageTokens * KD;
+        const bf16* vsrc = v_pages + ((size_t)page * G + kvh) * (size_t)kPageTokens * VD;
+        bf16* ks = kv_s + (size_t)stage * kStage;
+        bf16* vs = ks + MK * KD;
+        for (int i = threadIdx.x; i < MK * (KD / 8); i += 128) cp16(ks + i * 8, ksrc + i * 8);
+        for (int i = threadIdx.x; i < MK * (VD / 8); i += 128) cp16(vs + i * 8, vsrc + i * 8);
+    };
+    load_kv(kt_lo, 0);
+    cp_commit();
+
+    const float sk = sink != nullptr ? sink[head] : -INFINITY;
+    float m_run[2] = {sk, sk};
+    float l_run[2] = {(sink != nullptr && t4 == 0) ? 1.f : 0.f, (sink != nullptr && t4 == 0) ? 1.f : 0.f};
+    float o[VD / 8][4];
+#pragma unroll
+    for (int i = 0; i < VD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const uint32_t q_base = smem_u32(q_s);
+    const int qpos[2] = {p0 + warp * 16 + g, p0 + warp * 16 + g + 8};
+    int qlo[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        qlo[r] = chunk > 0 ? qpos[r] / chunk * chunk : 0;
+        if (window > 0) qlo[r] = max(qlo[r], qpos[r] + 1 - window);
+    }
+
+    for (int it = 0; it < n_kt; ++it) {
+        const int stage = it & 1;
+        if (it + 1 < n_kt) load_kv(kt_lo + it + 1, stage ^ 1);
+        cp_commit();
+        cp_wait<1>();
+        __syncthreads();
+        const uint32_t k_base = smem_u32(kv_s + (size_t)stage * kStage);
+        const uint32_t v_base = k_base + 2 * MK * KD;
+        const int key0 = (kt_lo + it) * MK;
+
+        float sc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KD / 16; ++kk) {
+            uint32_t qa[4];
+            {
+                const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(qa, q_base + 2 * tile_chunk_offset<KD>(row, kk * 2 + (lane >> 4)));
+            }
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                uint32_t b[4];
+                const int row = kb * 16 + (lane & 7) + (lane >> 4) * 8;
+                ldmatrix_x4(b, k_base + 2 * tile_chunk_offset<KD>(row, kk * 2 + ((lane >> 3) & 1)));
+                mma_bf16(sc[kb * 2], qa, b[0], b[1]);
+                mma_bf16(sc[kb * 2 + 1], qa, b[2], b[3]);
+            }
+        }
+        float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int key = key0 + nt * 8 + 2 * t4 + (i & 1);
+                const bool vis = key <= qpos[i >> 1] && key >= qlo[i >> 1];
+                const float s = vis ? sc[nt][i] * scale : -INFINITY;
+                sc[nt][i] = s;
+                m_new[i >> 1] = fmaxf(m_new[i >> 1], s);
+            }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+            m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+            m_use[r] = m_new[r] == -INFINITY ? 0.f : m_new[r];
+            corr[r] = __expf(m_run[r] - m_use[r]);
+            m_run[r] = m_new[r];
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < VD / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+            uint32_t hi[4], lo[4];
+            {
+                float p[2][4];
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        p[h][i] = __expf(sc[kb * 2 + h][i] - m_use[i >> 1]);
+                        l_run[i >> 1] += p[h][i];
+                    }
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float a = p[h][2 * j], b = p[h][2 * j + 1];
+                        const float ah = __bfloat162float(__float2bfloat16_rn(a)), bh = __bfloat162float(__float2bfloat16_rn(b));
+                        hi[h * 2 + j] = pack_bf16(ah, bh);
+                        lo[h * 2 + j] = pack_bf16(a - ah, b - bh);
+                    }
+            }
+#pragma unroll
+            for (int dd = 0; dd < VD / 16; ++dd) {
+                uint32_t vb[4];
+                const int row = kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4_trans(vb, v_base + 2 * tile_chunk_offset<VD>(row, dd * 2 + (lane >> 4)));
+                mma_bf16(o[dd * 2], hi, vb[0], vb[1]);
+                mma_bf16(o[dd * 2 + 1], hi, vb[2], vb[3]);
+                mma_bf16(o[dd * 2], lo, vb[0], vb[1]);
+                mma_bf16(o[dd * 2 + 1], lo, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int qi = warp * 16 + g + r * 8;
+        if (qi >= q_rows) continue;
+        const size_t row = (size_t)(row0 + q0 + qi);
+        float f = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+        if (gate != nullptr) f *= 1.f / (1.f + expf(-gate[row * gate_stride + head]));
+        bf16* op = out + (row * H + head) * VD;
+#pragma unroll
+        for (int i = 0; i < VD / 8; ++i)
+            *reinterpret_cast<uint32_t*>(op + i * 8 + 2 * t4) = pack_bf16(o[i][2 * r] * f, o[i][2 * r + 1] * f);
+    }
+}
+
+}  // namespace hos
+
+using namespace hos;
+
+// Head sizes of 64 or 128 numbers each (the caller runs the other kernel for the rest).
+// q: float32 [N][H][kd]; out: bfloat16 [N][H][vd]; n_q_tiles: at least the sum over sequences of ceil(rows / 64).
+extern "C" int hos_gated_attn_mma(const float* q, const void* k_pages, const void* v_pages, const int* page_table,
+                                  int table_stride, int ring_pages, const float* sink, const float* gate,
+                                  long long gate_stride, const int* cu_seqlens, const int* token_pos, const int* token_seq,
+                                  const int* seq_slot, void* out, int n_seqs, int n_q_tiles, int H, int G, int kd, int vd,
+                                  float scale, int chunk, int window, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_q_tiles <= 0) return 0;
+    if (G <= 0 || H % G != 0 || H > 65535) HOS_REFUSE("gated_attn_mma: %d heads over %d kv heads", H, G);
+    if ((kd != 64 && kd != 128) || (vd != 64 && vd != 128))
+        HOS_REFUSE("gated_attn_mma: heads of %d and %d numbers (64 or 128 are compiled)", kd, vd);
+    if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)out % 4))
+        HOS_REFUSE("gated_attn_mma: rows and pages must be 16-byte aligned");
+    const dim3 grid(n_q_tiles, H);
+#define HOS_GAM(KDv, VDv)                                                                                            \
+    do {                                                                                                             \
+        constexpr int smem = (MQ * KDv + 2 * MK * (KDv + VDv)) * 2;                                                  \
+        static bool attr_set = false;                                                                                \
+        if (!attr_set) {                                                                                             \
+            cudaFuncSetAttribute(gated_attn_mma_kernel<KDv, VDv>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+            attr_set = true;                                                                                         \
+        }                                                                                                            \
+        launch_pdl(gated_attn_mma_kernel<KDv, VDv>, grid, dim3(128), smem, stream, q, (const bf16*)k_pages,          \
+                   (const bf16*)v_pages, page_table, table_stride, ring_pages, sink, gate, gate_stride, cu_seqlens,  \
+                   token_pos, token_seq, seq_slot, (bf16*)out, n_seqs, H, G, scale, chunk, window);                  \
+    } while (0)
+    if (kd == 64 && vd == 64) HOS_GAM(64, 64);
+    else if (kd == 64) HOS_GAM(64, 128);
+    else if (vd == 64) HOS_GAM(128, 64);
+    else HOS_GAM(128, 128);
+#undef HOS_GAM
+    return check_launch("gated_attn_mma");
+}

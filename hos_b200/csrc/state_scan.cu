@@ -52,8 +52,18 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     float S[DR];
     float* st = state + (((size_t)slot * H + head) * vdim + (live ? col : 0)) * dim + r * DR;
     const bool fresh = token_pos[lo] == 0;
+    // a thread's run of rows is contiguous in the kept S^T: 16 bytes at a time where the run is whole and aligned
+    const bool whole = live && r * DR + DR <= dim && (dim & 3) == 0;
+    if (!fresh && whole) {
 #pragma unroll
-    for (int i = 0; i < DR; ++i) S[i] = (!fresh && live && r * DR + i < dim) ? st[i] : 0.f;
+        for (int i = 0; i < DR / 4; ++i) {
+            const float4 t = ((const float4*)st)[i];
+            S[4 * i] = t.x; S[4 * i + 1] = t.y; S[4 * i + 2] = t.z; S[4 * i + 3] = t.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DR; ++i) S[i] = (!fresh && live && r * DR + i < dim) ? st[i] : 0.f;
+    }
 
     for (int t0 = lo; t0 < hi; t0 += kScanChunk) {
         const int nt = min(kScanChunk, hi - t0);
@@ -91,20 +101,21 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                 const float gt = gs[t];
                 float u = c < CC ? vs[t * CC + c] : 0.f;
                 if (DELTA) {
-                    float dot = 0.f;
+                    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;       // four chains, not one of DR links
 #pragma unroll
                     for (int i = 0; i < DR / 4; ++i) {
                         const float4 kk = k4[i];
                         S[4 * i] *= gt; S[4 * i + 1] *= gt; S[4 * i + 2] *= gt; S[4 * i + 3] *= gt;
-                        dot = fmaf(S[4 * i], kk.x, dot);
-                        dot = fmaf(S[4 * i + 1], kk.y, dot);
-                        dot = fmaf(S[4 * i + 2], kk.z, dot);
-                        dot = fmaf(S[4 * i + 3], kk.w, dot);
+                        d0 = fmaf(S[4 * i], kk.x, d0);
+                        d1 = fmaf(S[4 * i + 1], kk.y, d1);
+                        d2 = fmaf(S[4 * i + 2], kk.z, d2);
+                        d3 = fmaf(S[4 * i + 3], kk.w, d3);
                     }
+                    float dot = (d0 + d1) + (d2 + d3);
                     for (int o = 1; o < R; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                     u = bs[t] * (u - dot);
                 }
-                float acc = 0.f;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < DR / 4; ++i) {
                     const float4 kk = k4[i], qq = q4[i];
@@ -119,11 +130,12 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                         S[4 * i + 2] = fmaf(gt, S[4 * i + 2], kk.z * u);
                         S[4 * i + 3] = fmaf(gt, S[4 * i + 3], kk.w * u);
                     }
-                    acc = fmaf(S[4 * i], qq.x, acc);
-                    acc = fmaf(S[4 * i + 1], qq.y, acc);
-                    acc = fmaf(S[4 * i + 2], qq.z, acc);
-                    acc = fmaf(S[4 * i + 3], qq.w, acc);
+                    a0 = fmaf(S[4 * i], qq.x, a0);
+                    a1 = fmaf(S[4 * i + 1], qq.y, a1);
+                    a2 = fmaf(S[4 * i + 2], qq.z, a2);
+                    a3 = fmaf(S[4 * i + 3], qq.w, a3);
                 }
+                float acc = (a0 + a1) + (a2 + a3);
                 for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                 if (r == 0 && c < CC) os[t * CC + c] = acc;
             }
@@ -134,7 +146,10 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             if (col0 + cc < vdim) out[((size_t)(t0 + t) * H + head) * vdim + col0 + cc] = os[idx];
         }
     }
-    if (live) {
+    if (whole) {
+#pragma unroll
+        for (int i = 0; i < DR / 4; ++i) ((float4*)st)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+    } else if (live) {
 #pragma unroll
         for (int i = 0; i < DR; ++i)
             if (r * DR + i < dim) st[i] = S[i];
@@ -246,6 +261,8 @@ extern "C" int hos_state_scan(const float* q, const float* k, const float* v, lo
     while (R * DR < dim) R <<= 1;
     int CC = 256 / R;
     if (CC > vdim) CC = vdim;
+    // few (sequence, head) pairs: fewer columns to a block, so that the blocks fill the GPU (columns are independent)
+    while (CC * R > 64 && (long long)n_seqs * H * ((vdim + CC - 1) / CC) < 2 * sm_count_cached()) CC = (CC + 1) / 2;
     const int threads = (CC * R + 31) / 32 * 32;
     const int dpad = R * (DR + kPad);
     const size_t smem = (size_t)(2 * kScanChunk * dpad + 2 * kScanChunk * CC + 2 * kScanChunk) * sizeof(float);

@@ -828,6 +828,25 @@ def gated_attn(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor]
                   cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), _stream())
 
 
+def gated_attn_mma(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                   gate_col: int, step, out: torch.Tensor, scale: float, chunk: int, window: int, n_q_tiles: int) -> bool:
+    """The same attention on the tensor cores, for bfloat16 caches and rows that come many to a sequence.  False: the
+    sizes are not that kernel's and nothing ran."""
+    n, heads, kd = q.shape
+    vd = cache.v_dim
+    if out.dtype != torch.bfloat16 or cache.k_pages.dtype != torch.bfloat16 or out.shape != (n, heads * vd):
+        return False
+    if kd not in (64, 128) or vd not in (64, 128) or q.data_ptr() % 16 or out.data_ptr() % 4:
+        return False
+    mixers().call("hos_gated_attn_mma", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
+                  cache.table_stride, cache.ring_pages, _ptr(sink),
+                  ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None,
+                  gate.shape[1] if gate is not None else 0, _ptr(step.cu_seqlens), _ptr(step.token_pos),
+                  _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), int(step.n_seqs), int(n_q_tiles), heads,
+                  cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), _stream())
+    return True
+
+
 def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_load: bool, g: torch.Tensor,
                per_token_g: bool, beta: Optional[torch.Tensor], state: torch.Tensor, step, out: torch.Tensor,
                heads: int, key_heads: int, dim: int, vdim: int) -> None:

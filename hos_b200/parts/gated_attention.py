@@ -12,7 +12,9 @@ and gate and attends over the other call's keys and values as the cache holds th
 Every row stores its key and value first and then attends over the cache, whether its sequence starts in this
 step or goes on: a position's result does not depend on how a prompt was cut.  The projections come out of
 one product in 32-bit; norms, angles, scores, weights and the weighted sums are 32-bit; the cache holds keys
-and values in the products' type.
+and values in the products' type.  In bfloat16, rows that come many to a sequence (more than FEW_TOKENS) run on
+the tensor cores where the head sizes are that kernel's (64 or 128): queries rounded to bfloat16, scores
+accumulated in 32-bit from exact products, the 32-bit weights fed as two bfloat16 terms.
 """
 from __future__ import annotations
 
@@ -24,13 +26,14 @@ from .. import ops
 from ..errors import KernelError, SpecError
 from ..registry import part_impl, register_part
 from . import linear
-from .base import CallStore, KVNeed, Mixer, StepInfo, WeightSpec
+from .base import FEW_TOKENS, CallStore, KVNeed, Mixer, StepInfo, WeightSpec
 
 SPLIT_MIN_KEYS = 256        # rows that see fewer keys are never cut into shares
 
 
 class GatedSoftmaxAttention(Mixer):
     graph_safe = True
+    use_tensor_cores = True      # tests switch it off to compare the two kernels on the same model
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -112,11 +115,13 @@ class GatedSoftmaxAttention(Mixer):
     def n_splits(self, n_rows: int, longest: int) -> int:
         """Into how many shares a row's keys are cut: only where the rows alone leave most of the GPU idle."""
         keys = self.keys_seen(longest)
-        warps = n_rows * self.n_heads
+        vpl = max(1, (self.vdim + 31) // 32)
+        together = next((c for c in (8, 4, 2) if (self.n_heads // self.n_kv_heads) % c == 0 and c * vpl <= 32), 1)
+        warps = n_rows * self.n_heads // together      # query heads that share a kv head go to one warp
         room = 8 * ops.sm_count()
         if keys < SPLIT_MIN_KEYS or warps >= room:
             return 1
-        return max(1, min(room // warps, keys // 128, 64))
+        return max(1, min(room // warps, keys // 64, 64))
 
     def forward(self, h, step: StepInfo, store: CallStore):
         return self._run(h, step, store, False)
@@ -139,6 +144,16 @@ class GatedSoftmaxAttention(Mixer):
                     getattr(self.position, "magnitude", 1.0), step, q, cache, self.n_heads,
                     0 if self.shares_kv else self.n_kv_heads, self.dim, self.vdim)
         att = torch.empty((n, self.n_heads * self.vdim), dtype=h.dtype, device=h.device)
+        gate = proj if self.head_gate else None
+        if self.use_tensor_cores and h.dtype == torch.bfloat16 and step.max_new > FEW_TOKENS:
+            # rows that come many to a sequence: 64 queries to a key tile on the tensor cores
+            if step.cu_host:
+                tiles = sum((step.cu_host[i + 1] - step.cu_host[i] + 63) // 64 for i in range(len(step.cu_host) - 1))
+            else:
+                tiles = (n + 63) // 64 + step.n_seqs
+            if ops.gated_attn_mma(q, cache, self.sink, gate, self.gate_col, step, att, self.scale, self.chunk or 0,
+                                  self.window or 0, tiles):
+                return linear.matmul_or_partials(att, self.w_o) if partial_ok else linear.matmul(att, self.w_o)
         ops.gated_attn(q, cache, self.sink, proj if self.head_gate else None, self.gate_col, step, att, self.scale,
                        self.chunk or 0, self.window or 0, self.n_splits(n, step.max_len_after))
         return linear.matmul_or_partials(att, self.w_o) if partial_ok else linear.matmul(att, self.w_o)

@@ -375,6 +375,27 @@ def test_generation_through_the_command_line(folders):
         seq.append(t)
 
 
+def test_the_two_attention_kernels_agree_in_bfloat16(folders):
+    """The tensor-core kernel against the FMA kernel on the same bfloat16 model: a prompt, a piece, single tokens."""
+    from hos_b200.parts.gated_attention import GatedSoftmaxAttention
+    vocab = CASES["E"][0]["vocab"]
+    seq = tokens(130, 400, vocab)
+    outs = []
+    for use in (True, False):
+        GatedSoftmaxAttention.use_tensor_cores = use
+        try:
+            r = _runner(folders["E"], "bfloat16")
+            (slot,) = r.admit(1)
+            got = [r.step([slot], [seq[:310]], [list(range(0, 310, 3))]), r.step([slot], [seq[310:380]], [list(range(70))])]
+            got += [r.step([slot], [[t]]) for t in seq[380:]]
+            outs.append(torch.cat(got).cpu())
+            r.release(slot)
+        finally:
+            GatedSoftmaxAttention.use_tensor_cores = True
+    assert_rows(outs[0], outs[1], "bfloat16", "the two kernels")       # one more rounding (the queries), as far apart as
+                                                                       # either is from the oracle at most
+
+
 def test_the_kernels_alone_against_float64():
     """The attention kernel (one share and several) and the state scan (both rules) on random rows, without a model
     around them: keys and values of unequal sizes in a paged cache whose pages lie in no order."""
@@ -405,6 +426,56 @@ def test_the_kernels_alone_against_float64():
         out = torch.empty(n, H * vd, device=dev)
         ops.gated_attn(q, cache, sink, gate, 3, step, out, scale, chunk, 0, splits)
         assert float((out.cpu().double().view(n, H, vd) - want).abs().max()) < 2e-5, f"{splits} shares"
+    # the tensor-core kernel: bfloat16 cache and output, three sequences of which one goes on from position 100, head
+    # sizes 64/128 both ways round; its error is the rounding of q, k, v and of the output to bfloat16
+    for kd2, vd2 in ((64, 128), (128, 64), (128, 128), (64, 64)):
+        lens, starts = (150, 70, 3), (0, 100, 0)
+        tot = [a + b for a, b in zip(lens, starts)]
+        n2 = sum(lens)
+        q2 = torch.randn(n2, H, kd2, device=dev)
+        pages_of, table, nxt = [], torch.zeros(3, 4, dtype=torch.int32), 1
+        for sq, t in enumerate(tot):
+            for e in range((t + 63) // 64):
+                table[sq, e] = nxt
+                nxt += 2                                   # pages lie apart
+        kp2 = torch.zeros(nxt + 1, G, 64, kd2, device=dev, dtype=torch.bfloat16)
+        vp2 = torch.zeros(nxt + 1, G, 64, vd2, device=dev, dtype=torch.bfloat16)
+        ks = [torch.randn(t, G, kd2).to(torch.bfloat16) for t in tot]
+        vs = [torch.randn(t, G, vd2).to(torch.bfloat16) for t in tot]
+        from hos_b200.parts.gated_attention import GatedSoftmaxAttention  # noqa: F401  (the layout helper below is the cache's)
+
+        def place(pages, rows, hd):
+            for sq, r in enumerate(rows):
+                for t in range(r.shape[0]):
+                    for d0 in range(0, hd, 8):             # the cache's permutation of 16-byte groups
+                        c = (d0 // 8) ^ (t % 64 % 8)
+                        pages[table[sq, t // 64], :, t % 64, c * 8:c * 8 + 8] = r[t, :, d0:d0 + 8].to(dev)
+        place(kp2, ks, kd2)
+        place(vp2, vs, vd2)
+        cache2 = ops.PagedKVArgs(kp2, vp2, table.to(dev), 0, G, kd2, vd2)
+        pos2 = torch.cat([s0 + torch.arange(ln) for s0, ln in zip(starts, lens)]).to(torch.int32).to(dev)
+        seq2 = torch.cat([torch.full((ln,), i) for i, ln in enumerate(lens)]).to(torch.int32).to(dev)
+        cu2 = torch.tensor([0, 150, 220, 223], dtype=torch.int32, device=dev)
+        gate2 = torch.randn(n2, H, device=dev)
+        step2 = StepInfo(n2, 3, None, pos2, seq2, cu2, torch.arange(3, dtype=torch.int32, device=dev), None, False, False, 150, 170)
+        want2, at = [], 0
+        qb = q2.to(torch.bfloat16).double().cpu()
+        for sq, (ln, s0) in enumerate(zip(lens, starts)):
+            kk, vv = ks[sq].double().repeat_interleave(H // G, 1), vs[sq].double().repeat_interleave(H // G, 1)
+            sc = torch.einsum("ihd,jhd->hij", qb[at:at + ln], kk) * scale
+            ii, jj = (s0 + torch.arange(ln))[:, None], torch.arange(tot[sq])[None]
+            sc = sc.masked_fill(~((ii >= jj) & (ii // chunk == jj // chunk)), float("-inf"))
+            pr = torch.softmax(torch.cat([sc, sink.double().cpu().view(H, 1, 1).expand(H, ln, 1)], -1), -1)[..., :tot[sq]]
+            want2.append(torch.einsum("hij,jhr->ihr", pr, vv) * torch.sigmoid(gate2[at:at + ln].double().cpu())[..., None])
+            at += ln
+        want2 = torch.cat(want2)
+        out2 = torch.empty(n2, H * vd2, device=dev, dtype=torch.bfloat16)
+        assert ops.gated_attn_mma(q2, cache2, sink, gate2, 0, step2, out2, scale, chunk, 0, 3 + 2 + 1)
+        err = (out2.double().cpu().view(n2, H, vd2) - want2).abs().max()
+        assert float(err) < 1e-2, f"tensor-core kernel, heads of {kd2}/{vd2}: {float(err):.2e}"
+        ref = torch.empty(n2, H * vd2, device=dev, dtype=torch.bfloat16)
+        ops.gated_attn(q2.to(torch.bfloat16).float(), cache2, sink, gate2, 0, step2, ref, scale, chunk, 0, 1)
+        assert float((out2.float() - ref.float()).abs().max()) < 1e-2
     # the scans: two sequences in one step, the second resuming from a state
     for rule in ("decay", "delta"):
         Hh, Gk, d, vdim = 4, 2 if rule == "delta" else 4, 20, 12
