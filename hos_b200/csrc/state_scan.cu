@@ -9,7 +9,9 @@
 //
 // state_scan: one block per (sequence, head, run of value columns); a column of S is cut into R runs of DR rows,
 //   one thread each (R lanes side by side, so that sums over a column are shuffles); tokens in order, a chunk of
-//   them staged in shared memory at a time.  Columns are independent of one another in both rules.
+//   them staged in shared memory while the chunk before it is walked (cp.async, two buffers).  Columns are
+//   independent of one another in both rules.
+// act_rows: x logistic(x) in place on the leading columns of 32-bit rows (the decay rule's q, k, v).
 // conv_prep (the delta rule's inputs): per token, the short causal convolution over time of the q, k, v
 //   projections (per channel, `taps` wide, the last tap the current token's, the inputs before a step's first
 //   row from the slot's state), x sigmoid(x) of it, q and k divided by their length per head
@@ -24,10 +26,28 @@ constexpr int kPad = 4;             // floats after every DR staged numbers: 16-
 
 __device__ __forceinline__ float silu_precise(float x) { return x / (1.f + expf(-x)); }
 
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_all() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// x <- x logistic(x) on the first `cols` numbers of every row (the decay rule's q, k, v before the scan)
+__global__ void act_rows_kernel(float* __restrict__ x, long long ld, int cols, long long n) {
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float* p = x + (i / cols) * ld + (i % cols);
+    *p = silu_precise(*p);
+}
+
 template <int DR, bool DELTA>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long long ld,
-                  int silu_on_load, const float* __restrict__ g, long long g_ld, const float* __restrict__ beta,
+                  int aligned, const float* __restrict__ g, long long g_ld, const float* __restrict__ beta,
                   long long beta_ld, float* __restrict__ state, const int* __restrict__ token_pos,
                   const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                   float* __restrict__ out, int H, int Gk, int dim, int vdim, int R, int CC) {
@@ -42,12 +62,10 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     const int col = col0 + c;
     const bool live = c < CC && col < vdim;
     const int dpad = R * (DR + kPad);
-    float* qs = sm;                              // [chunk][dpad]
-    float* ks = qs + kScanChunk * dpad;          // [chunk][dpad]
-    float* vs = ks + kScanChunk * dpad;          // [chunk][CC]
-    float* gs = vs + kScanChunk * CC;            // [chunk]
-    float* bs = gs + kScanChunk;                 // [chunk]
-    float* os = bs + kScanChunk;                 // [chunk][CC]
+    // two buffers of staged tokens: while one chunk is walked the next one's rows are on their way (cp.async)
+    const int per_buf = kScanChunk * (2 * dpad + 2 * CC) + 2 * kScanChunk;      // q, k, v, o, g, beta
+    const int CC4 = (CC + 3) & ~3;
+    (void)CC4;
 
     float S[DR];
     float* st = state + (((size_t)slot * H + head) * vdim + (live ? col : 0)) * dim + r * DR;
@@ -64,36 +82,56 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 #pragma unroll
         for (int i = 0; i < DR; ++i) S[i] = (!fresh && live && r * DR + i < dim) ? st[i] : 0.f;
     }
+    for (int i = threadIdx.x; i < 2 * per_buf; i += blockDim.x) sm[i] = 0.f;     // the padding stays zero for good
+    __syncthreads();
 
-    for (int t0 = lo; t0 < hi; t0 += kScanChunk) {
-        const int nt = min(kScanChunk, hi - t0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * R * DR; idx += blockDim.x) {
-            const int t = idx / (R * DR), d = idx % (R * DR);
-            float qv = 0.f, kv = 0.f;
-            if (d < dim) {
-                qv = q[(size_t)(t0 + t) * ld + kh * dim + d];
-                kv = k[(size_t)(t0 + t) * ld + kh * dim + d];
-                if (silu_on_load) {
-                    qv = silu_precise(qv);
-                    kv = silu_precise(kv);
-                }
+    auto stage = [&](int t0, int nt, float* buf) {
+        float* qs = buf;
+        float* ks = qs + kScanChunk * dpad;
+        float* vs = ks + kScanChunk * dpad;
+        float* gs = vs + 2 * kScanChunk * CC;        // after v and o
+        float* bs = gs + kScanChunk;
+        if (aligned) {
+            const int d4 = dim >> 2;
+            for (int idx = threadIdx.x; idx < nt * d4; idx += blockDim.x) {
+                const int t = idx / d4, d = (idx % d4) << 2;
+                const int at = t * dpad + d + (d / DR) * kPad;
+                cp_async16(qs + at, q + (size_t)(t0 + t) * ld + kh * dim + d);
+                cp_async16(ks + at, k + (size_t)(t0 + t) * ld + kh * dim + d);
             }
-            const int at = t * dpad + d + (d / DR) * kPad;
-            qs[at] = qv;
-            ks[at] = kv;
+        } else {
+            for (int idx = threadIdx.x; idx < nt * dim; idx += blockDim.x) {
+                const int t = idx / dim, d = idx % dim;
+                const int at = t * dpad + d + (d / DR) * kPad;
+                cp_async4(qs + at, q + (size_t)(t0 + t) * ld + kh * dim + d);
+                cp_async4(ks + at, k + (size_t)(t0 + t) * ld + kh * dim + d);
+            }
         }
-        for (int idx = threadIdx.x; idx < nt * CC; idx += blockDim.x) {
-            const int t = idx / CC, cc = idx % CC;
-            float vv = col0 + cc < vdim ? v[(size_t)(t0 + t) * ld + head * vdim + col0 + cc] : 0.f;
-            if (silu_on_load) vv = silu_precise(vv);
-            vs[idx] = vv;
+        const int ncol = min(CC, vdim - col0);
+        for (int idx = threadIdx.x; idx < nt * ncol; idx += blockDim.x) {
+            const int t = idx / ncol, cc = idx % ncol;
+            cp_async4(vs + t * CC + cc, v + (size_t)(t0 + t) * ld + head * vdim + col0 + cc);
         }
         if (threadIdx.x < nt) {
-            gs[threadIdx.x] = g[(size_t)(t0 + threadIdx.x) * g_ld + head];
-            bs[threadIdx.x] = DELTA ? beta[(size_t)(t0 + threadIdx.x) * beta_ld + head] : 1.f;
+            cp_async4(gs + threadIdx.x, g + (size_t)(t0 + threadIdx.x) * g_ld + head);
+            if (DELTA) cp_async4(bs + threadIdx.x, beta + (size_t)(t0 + threadIdx.x) * beta_ld + head);
         }
-        __syncthreads();
+        cp_async_commit_all();
+    };
+
+    stage(lo, min(kScanChunk, hi - lo), sm);
+    int which = 0;
+    for (int t0 = lo; t0 < hi; t0 += kScanChunk, which ^= 1) {
+        const int nt = min(kScanChunk, hi - t0);
+        cp_async_wait_all();
+        __syncthreads();            // this chunk has landed; everyone is done with the other buffer
+        if (t0 + kScanChunk < hi) stage(t0 + kScanChunk, min(kScanChunk, hi - t0 - kScanChunk), sm + (which ^ 1) * per_buf);
+        float* qs = sm + which * per_buf;
+        float* ks = qs + kScanChunk * dpad;
+        float* vs = ks + kScanChunk * dpad;
+        float* os = vs + kScanChunk * CC;
+        float* gs = os + kScanChunk * CC;
+        float* bs = gs + kScanChunk;
         {       // every thread walks (a warp's shuffles want all its lanes); only live columns are written
             for (int t = 0; t < nt; ++t) {
                 const float4* k4 = (const float4*)(ks + t * dpad + r * (DR + kPad));
@@ -249,30 +287,36 @@ using namespace hos;
 // q, k: rows of Gk heads of `dim` numbers; v: rows of H heads of `vdim`; all float32 with `ld` numbers between rows.
 // g: [.][H] with g_ld between rows (0: one row of constants).  beta: null for the decay rule.  state: [slots][H][vdim][dim].
 // out: float32 [N][H][vdim].
-extern "C" int hos_state_scan(const float* q, const float* k, const float* v, long long ld, int silu_on_load, const float* g,
+extern "C" int hos_state_scan(const float* q, const float* k, const float* v, long long ld, const float* g,
                               long long g_ld, const float* beta, long long beta_ld, float* state, const int* token_pos,
-                              const int* token_seq, const int* cu_seqlens, const int* seq_slot, float* out, int n_seqs, int H,
-                              int Gk, int dim, int vdim, cudaStream_t stream) {
+                              const int* token_seq, const int* cu_seqlens, const int* seq_slot, float* out, int n_rows,
+                              int n_seqs, int H, int Gk, int dim, int vdim, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (Gk <= 0 || H % Gk != 0) HOS_REFUSE("state_scan: %d heads are not a multiple of %d key heads", H, Gk);
     if (dim <= 0 || dim > 1024 || vdim <= 0) HOS_REFUSE("state_scan: heads of %d x %d", dim, vdim);
-    const int DR = dim <= 16 ? 4 : (dim <= 64 ? 8 : (dim <= 512 ? 16 : 32));
+    // short runs of rows per thread: a token's walk is a chain of dependent instructions (scale, dot, sum over the
+    // runs, update, read-out, sum), and with few (sequence, head) pairs nothing else hides its latency; the sums over
+    // 16 or 32 runs are shuffles
+    const int DR = dim <= 16 ? 4 : (dim <= 256 ? 8 : (dim <= 512 ? 16 : 32));
     int R = 1;
     while (R * DR < dim) R <<= 1;
     int CC = 256 / R;
     if (CC > vdim) CC = vdim;
-    // few (sequence, head) pairs: fewer columns to a block, so that the blocks fill the GPU (columns are independent)
-    while (CC * R > 64 && (long long)n_seqs * H * ((vdim + CC - 1) / CC) < 2 * sm_count_cached()) CC = (CC + 1) / 2;
+    // single tokens and few (sequence, head) pairs: fewer columns to a block, so that the blocks fill the GPU (columns
+    // are independent; every block stages the whole q and k rows, which a long walk would pay for token by token)
+    if (n_rows <= 2 * n_seqs)
+        while (CC * R > 64 && (long long)n_seqs * H * ((vdim + CC - 1) / CC) < 2 * sm_count_cached()) CC = (CC + 1) / 2;
     const int threads = (CC * R + 31) / 32 * 32;
     const int dpad = R * (DR + kPad);
-    const size_t smem = (size_t)(2 * kScanChunk * dpad + 2 * kScanChunk * CC + 2 * kScanChunk) * sizeof(float);
+    const size_t smem = (size_t)2 * (2 * kScanChunk * dpad + 2 * kScanChunk * CC + 2 * kScanChunk) * sizeof(float);
+    const int aligned = (dim % 4 == 0 && ld % 4 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0) ? 1 : 0;
     const dim3 grid(n_seqs, H, (vdim + CC - 1) / CC);
     const bool delta = beta != nullptr;
     if (smem > 200 * 1024) HOS_REFUSE("state_scan: heads of %d x %d do not fit a block's shared memory", dim, vdim);
 #define HOS_SCAN(DRv, DL)                                                                                            \
     if (smem > 48 * 1024)                                                                                            \
         cudaFuncSetAttribute(state_scan_kernel<DRv, DL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    launch_pdl(state_scan_kernel<DRv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, silu_on_load, g, g_ld, beta, \
+    launch_pdl(state_scan_kernel<DRv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, aligned, g, g_ld, beta, \
                beta_ld, state, token_pos, token_seq, cu_seqlens, seq_slot, out, H, Gk, dim, vdim, R, CC)
 #define HOS_SCAN_D(DRv)                                                                                              \
     do {                                                                                                             \
@@ -286,6 +330,13 @@ extern "C" int hos_state_scan(const float* q, const float* k, const float* v, lo
 #undef HOS_SCAN_D
 #undef HOS_SCAN
     return check_launch("state_scan");
+}
+
+extern "C" int hos_act_rows(float* x, long long ld, int cols, int N, cudaStream_t stream) {
+    const long long n = (long long)N * cols;
+    if (n <= 0) return 0;
+    launch_pdl(act_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, ld, cols, n);
+    return check_launch("act_rows");
 }
 
 // act: float32 [N][2 Gk dim + H vdim] (q, k, v after convolution, activation and lengths); beta_out, g_out: [N][H].

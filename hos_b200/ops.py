@@ -861,10 +861,14 @@ def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_l
     if out.shape != (n, heads * vdim) or tuple(state.shape[1:]) != (heads, vdim, dim):
         raise KernelError("state_scan: sizes disagree")
     base = rows.data_ptr()
+    if silu_on_load:        # q, k, v lie side by side from q_col on: x logistic(x) in place, once, before the walk
+        if not (q_col < k_col < v_col) or v_col + heads * vdim - q_col != 2 * key_heads * dim + heads * vdim:
+            raise KernelError("state_scan: q, k, v must lie side by side for the activation")
+        mixers().call("hos_act_rows", ctypes.c_void_p(base + 4 * q_col), ld, 2 * key_heads * dim + heads * vdim, n, _stream())
     mixers().call("hos_state_scan", ctypes.c_void_p(base + 4 * q_col), ctypes.c_void_p(base + 4 * k_col),
-                  ctypes.c_void_p(base + 4 * v_col), ld, 1 if silu_on_load else 0, _ptr(g), heads if per_token_g else 0,
+                  ctypes.c_void_p(base + 4 * v_col), ld, _ptr(g), heads if per_token_g else 0,
                   _ptr(beta), heads if beta is not None else 0, _ptr(state), _ptr(step.token_pos), _ptr(step.token_seq),
-                  _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out), int(step.n_seqs), int(heads), int(key_heads),
+                  _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out), n, int(step.n_seqs), int(heads), int(key_heads),
                   int(dim), int(vdim), _stream())
 
 
