@@ -395,9 +395,10 @@ def vagonex_kernel_work(z, tokens, batch, ctx):
 
     def scan(n, seqs):        # rows in and out, the state in and out; S update and read-out: 4 (decay) to 7 (delta) per cell
         return n * (cols + sh * sv) * 4 + seqs * sh * sd * sv * 4 * 2, 7.0 * n * sh * sd * sv
+    attn = {"prefill": (tokens * G * (kd + vd) * 2 + tokens * H * (kd * 4 + vd * 2), 2.0 * pairs * H * (kd + vd)),
+            "decode": (batch * keys * G * (kd + vd) * 2, 2.0 * batch * keys * H * (kd + vd))}
     return {
-        "hos_gated_attn": {"prefill": (tokens * G * (kd + vd) * 2 + tokens * H * (kd * 4 + vd * 2), 2.0 * pairs * H * (kd + vd)),
-                           "decode": (batch * keys * G * (kd + vd) * 2, 2.0 * batch * keys * H * (kd + vd))},
+        "hos_gated_attn": attn, "hos_gated_attn_mma": attn, "hos_gated_attn_mma_decode": attn,
         "hos_state_scan": {"prefill": scan(tokens, 1), "decode": scan(batch, batch)},
         "hos_qk_prep": {"prefill": (tokens * (H * kd * 8 + G * (kd + vd) * 6), 0.0),
                         "decode": (batch * (H * kd * 8 + G * (kd + vd) * 6), 0.0)},

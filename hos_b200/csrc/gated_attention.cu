@@ -396,3 +396,13 @@ extern "C" int hos_gated_attn(const float* q, void* k_pages, void* v_pages, int 
                (const float*)part_ml, n_splits, gate, gate_stride, token_seq, out, out_bf16, N, H, vd);
     return check_launch("attn_merge");
 }
+
+// The shares' partial results under one maximum: out [N][H][vd] from part_acc [N][H][n_splits][vd], part_ml [..][2].
+extern "C" int hos_attn_merge(const float* part_acc, const float* part_ml, int n_splits, const float* gate,
+                              long long gate_stride, const int* token_seq, void* out, int out_dtype, int N, int H, int vd,
+                              cudaStream_t stream) {
+    if (N <= 0) return 0;
+    launch_pdl(attn_merge_kernel, dim3((unsigned)(((long long)N * H + 3) / 4)), dim3(128), 0, stream, part_acc, part_ml,
+               n_splits, gate, gate_stride, token_seq, out, out_dtype == kBF16 ? 1 : 0, N, H, vd);
+    return check_launch("attn_merge");
+}

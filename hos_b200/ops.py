@@ -847,6 +847,33 @@ def gated_attn_mma(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Ten
     return True
 
 
+def gated_attn_mma_decode(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                          gate_col: int, step, out: torch.Tensor, scale: float, chunk: int, window: int,
+                          n_splits: int = 1) -> bool:
+    """Single tokens on the tensor cores: the query heads that share a kv head are the rows of one tile.  False: the
+    sizes are not that kernel's and nothing ran."""
+    n, heads, kd = q.shape
+    vd = cache.v_dim
+    if out.dtype != torch.bfloat16 or cache.k_pages.dtype != torch.bfloat16 or out.shape != (n, heads * vd):
+        return False
+    if kd not in (64, 128) or vd not in (64, 128) or heads // cache.n_kv_heads > 16 or q.data_ptr() % 16:
+        return False
+    part_acc = part_ml = None
+    if n_splits > 1:
+        part_acc = torch.empty((n, heads, n_splits, vd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    gate_ptr = ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None
+    gate_ld = gate.shape[1] if gate is not None else 0
+    mixers().call("hos_gated_attn_mma_decode", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
+                  cache.table_stride, cache.ring_pages, _ptr(sink), gate_ptr, gate_ld, _ptr(step.token_pos),
+                  _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), _ptr(part_acc), _ptr(part_ml), int(n_splits), n,
+                  heads, cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), _stream())
+    if n_splits > 1:
+        mixers().call("hos_attn_merge", _ptr(part_acc), _ptr(part_ml), int(n_splits), gate_ptr, gate_ld,
+                      _ptr(step.token_seq), _ptr(out), dtype_code(out.dtype), n, heads, vd, _stream())
+    return True
+
+
 def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_load: bool, g: torch.Tensor,
                per_token_g: bool, beta: Optional[torch.Tensor], state: torch.Tensor, step, out: torch.Tensor,
                heads: int, key_heads: int, dim: int, vdim: int) -> None:

@@ -14,7 +14,9 @@ step or goes on: a position's result does not depend on how a prompt was cut.  T
 one product in 32-bit; norms, angles, scores, weights and the weighted sums are 32-bit; the cache holds keys
 and values in the products' type.  In bfloat16, rows that come many to a sequence (more than FEW_TOKENS) run on
 the tensor cores where the head sizes are that kernel's (64 or 128): queries rounded to bfloat16, scores
-accumulated in 32-bit from exact products, the 32-bit weights fed as two bfloat16 terms.
+accumulated in 32-bit from exact products, the 32-bit weights fed as two bfloat16 terms.  Single tokens run there
+too (up to 16 query heads to a kv head: they are the rows of one tile, the key tiles cut into shares where the
+rows alone would leave the GPU idle); steps of 2 to FEW_TOKENS tokens and all other sizes keep the FMA kernel.
 """
 from __future__ import annotations
 
@@ -153,6 +155,13 @@ class GatedSoftmaxAttention(Mixer):
                 tiles = (n + 63) // 64 + step.n_seqs
             if ops.gated_attn_mma(q, cache, self.sink, gate, self.gate_col, step, att, self.scale, self.chunk or 0,
                                   self.window or 0, tiles):
+                return linear.matmul_or_partials(att, self.w_o) if partial_ok else linear.matmul(att, self.w_o)
+        if self.use_tensor_cores and h.dtype == torch.bfloat16 and step.max_new == 1:
+            # single tokens: the query heads of a kv head are the rows of one tile; few rows: the key tiles in shares
+            tiles = (self.keys_seen(step.max_len_after) + 63) // 64 + 1
+            shares = max(1, min(tiles, 2 * ops.sm_count() // max(1, n * self.n_kv_heads), 32))
+            if ops.gated_attn_mma_decode(q, cache, self.sink, gate, self.gate_col, step, att, self.scale, self.chunk or 0,
+                                         self.window or 0, shares):
                 return linear.matmul_or_partials(att, self.w_o) if partial_ok else linear.matmul(att, self.w_o)
         ops.gated_attn(q, cache, self.sink, proj if self.head_gate else None, self.gate_col, step, att, self.scale,
                        self.chunk or 0, self.window or 0, self.n_splits(n, step.max_len_after))

@@ -476,6 +476,17 @@ def test_the_kernels_alone_against_float64():
         ref = torch.empty(n2, H * vd2, device=dev, dtype=torch.bfloat16)
         ops.gated_attn(q2.to(torch.bfloat16).float(), cache2, sink, gate2, 0, step2, ref, scale, chunk, 0, 1)
         assert float((out2.float() - ref.float()).abs().max()) < 1e-2
+        # single tokens on the tensor cores: the last token of each of the three sequences, one share and several
+        last = [149, 219, 222]
+        q1, g1 = q2[last].contiguous(), gate2[last].contiguous()
+        step1 = StepInfo(3, 3, None, pos2[last].contiguous(), torch.arange(3, dtype=torch.int32, device=dev),
+                         torch.arange(4, dtype=torch.int32, device=dev), torch.arange(3, dtype=torch.int32, device=dev), None,
+                         False, True, 1, 170)
+        for shares in (1, 2, 5):
+            out1 = torch.empty(3, H * vd2, device=dev, dtype=torch.bfloat16)
+            assert ops.gated_attn_mma_decode(q1, cache2, sink, g1, 0, step1, out1, scale, chunk, 0, shares)
+            err = (out1.double().cpu().view(3, H, vd2) - want2[last]).abs().max()
+            assert float(err) < 1e-2, f"single tokens, heads of {kd2}/{vd2}, {shares} shares: {float(err):.2e}"
     # the scans: two sequences in one step, the second resuming from a state
     for rule in ("decay", "delta"):
         Hh, Gk, d, vdim = 4, 2 if rule == "delta" else 4, 20, 12
