@@ -413,6 +413,38 @@ DESIGNS = {"satapel": lambda: (SATAPEL_SIZES, satapel_raw, gemma_raw_like, satap
                                ("hos_state_scan", "hos_gated_attn"))}
 
 
+def run_design_profile_step(args) -> int:
+    """For a profiler: one block of the design's layers (4 layers at the first of --sizes), two steps of the asked kind
+    launched kernel by kernel (no CUDA graph): a prompt of --prefill-tokens tokens, or a single-token step of the last
+    of --batches sequences that hold --ctx tokens.  Holds about 1 GB on the device.  Prints "ok"."""
+    import random
+    import torch
+    from hos_b200 import Engine
+    from hos_b200.registry import config_from_dict
+    sizes, raw_of, _, _, _ = DESIGNS[args.design]()
+    z = dict(sizes[args.sizes.split(",")[0]], blocks=1)
+    b = int(args.batches.split(",")[-1])
+    ctx = args.ctx if args.ctx != 8192 else 1024
+    eng = Engine.from_config(config_from_dict(raw_of(z)), seed=0, dtype="bfloat16", max_batch=b,
+                             max_tokens=b * (ctx + 64) + args.prefill_tokens + 64, max_seq_len=max(ctx, args.prefill_tokens) + 64)
+    r, rng = eng.runner, random.Random(0)
+    r.use_sessions = False
+    if args.profile == "prefill":
+        for _ in range(2):
+            s = r.admit(1)
+            r.step(s, [[rng.randrange(r.vocab_size) for _ in range(args.prefill_tokens)]])
+            r.release(s[0])
+    else:
+        s = r.admit(b)
+        r.cache.extend_all(s, [ctx - 2] * b)
+        r.write_records(s, pos=[ctx - 2] * b)
+        for _ in range(2):
+            r.step(s, [[rng.randrange(r.vocab_size)] for _ in range(b)])
+    torch.cuda.synchronize()
+    print("ok")
+    return 0
+
+
 def run_design_comparison(args) -> int:
     """Prompt and decode throughput of Satapel beside Gemma-2 at equal size, and where each of the design's own
     kernels stands against its roofline: the larger of (bytes over the measured copy rate) and (the FLOPs of the
@@ -522,6 +554,9 @@ def main() -> int:
     ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="not the driver's line: prompt and decode throughput of this design beside Gemma-2 at equal "
                          "size, with its kernels against their rooflines (--sizes, --batches, --ctx, --prefill-tokens)")
+    ap.add_argument("--profile", default=None, choices=["prefill", "decode"],
+                    help="with --design: no measurement, just two steps of that kind of one block of layers, kernel by "
+                         "kernel, for a profiler to capture")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of the sizes s, m, l")
     ap.add_argument("--batches", default="1,8,64", help="with --design: decode batch sizes")
     args = ap.parse_args()
@@ -536,6 +571,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design and args.profile:
+        return run_design_profile_step(args)
     if args.design:
         return run_design_comparison(args)
     if args.workload == "baseline":

@@ -133,7 +133,11 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         float* gs = os + kScanChunk * CC;
         float* bs = gs + kScanChunk;
         {       // every thread walks (a warp's shuffles want all its lanes); only live columns are written
-            for (int t = 0; t < nt; ++t) {
+            float part[kScanChunk];       // the read-outs' partial sums: added up after the walk, off its chain
+#pragma unroll
+            for (int t = 0; t < kScanChunk; ++t) {
+                part[t] = 0.f;
+                if (t >= nt) continue;
                 const float4* k4 = (const float4*)(ks + t * dpad + r * (DR + kPad));
                 const float4* q4 = (const float4*)(qs + t * dpad + r * (DR + kPad));
                 const float gt = gs[t];
@@ -173,7 +177,12 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                     a2 = fmaf(S[4 * i + 2], qq.z, a2);
                     a3 = fmaf(S[4 * i + 3], qq.w, a3);
                 }
-                float acc = (a0 + a1) + (a2 + a3);
+                part[t] = (a0 + a1) + (a2 + a3);
+            }
+#pragma unroll
+            for (int t = 0; t < kScanChunk; ++t) {
+                if (t >= nt) break;
+                float acc = part[t];
                 for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                 if (r == 0 && c < CC) os[t * CC + c] = acc;
             }

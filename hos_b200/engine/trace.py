@@ -25,13 +25,17 @@ from typing import Dict
 
 
 
+SLACK_REQUESTS = 64
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to 64")
+                    help="most tokens live requests hold at any time (the cache keeps a page of 64 more per request, for "
+                         "up to 64 requests, in case the count was not rounded up to pages)")
     ap.add_argument("--chunk-tokens", type=int, default=2048,
                     help="most tokens one pass adds to a request that is under way (more are run as several "
                          "passes); layers with a window keep a ring of window + this many keys")
@@ -43,7 +47,9 @@ def main(argv=None) -> int:
     from .runner import Runner
     # the cache alone bounds a request's length here: replay is not cut at the model's
     # max_position_embeddings, which generation takes as its context limit
-    runner = Runner.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
+    # every live request's count is rounded up to a page of 64 by the cache: a caller that counted bare tokens gets
+    # the pages of 64 more requests on top
+    runner = Runner.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens + SLACK_REQUESTS * 64,
                                 max_seq_len=args.max_tokens, chunk_tokens=args.chunk_tokens)
     slots: Dict[str, int] = {}
 
