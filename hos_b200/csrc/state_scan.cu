@@ -82,8 +82,11 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 #pragma unroll
         for (int i = 0; i < DR; ++i) S[i] = (!fresh && live && r * DR + i < dim) ? st[i] : 0.f;
     }
-    for (int i = threadIdx.x; i < 2 * per_buf; i += blockDim.x) sm[i] = 0.f;     // the padding stays zero for good
-    __syncthreads();
+    // rows beyond dim and columns beyond vdim are read by the walk and never staged: they stay zero for good
+    if (R * DR != dim || col0 + CC > vdim) {
+        for (int i = threadIdx.x; i < 2 * per_buf; i += blockDim.x) sm[i] = 0.f;
+        __syncthreads();
+    }
 
     auto stage = [&](int t0, int nt, float* buf) {
         float* qs = buf;

@@ -56,7 +56,7 @@ def test_the_rotary_table_with_the_ramp():
     from hos_b200.parts.base import Runtime
     from hos_b200.parts.rope import Rotary
     rt = Runtime(torch.device("cpu"), torch.float32)
-    for rot in ({"base": 20000.0, "dims": 48, "scaling": {"factor": 4.0, "original": 128, "fast": 32.0, "slow": 1.0}},
+    for rot in ({"base": 30000.0, "dims": 40, "scaling": {"factor": 3.0, "original": 96, "fast": 24.0, "slow": 1.5}},
                 {"base": 100.0, "dims": 16, "scaling": {"factor": 16.0, "original": 32, "fast": 3.0, "slow": 1.5}},
                 {"base": 10000.0, "dims": 8, "scaling": {"factor": 8.0, "original": 64, "fast": 16.0, "slow": 2.0}},
                 {"base": 500.0, "dims": 6}):
@@ -65,10 +65,10 @@ def test_the_rotary_table_with_the_ramp():
         freqs, mult = P.rotary_table(rot)
         assert abs(part.magnitude - mult) < 1e-12
         assert torch.allclose(part.inv_freq.double(), torch.tensor(freqs, dtype=torch.float64), rtol=1e-7, atol=0)
-    ramped, _ = P.rotary_table({"base": 20000.0, "dims": 48, "scaling": {"factor": 4.0, "original": 128, "fast": 32.0, "slow": 1.0}})
-    plain, _ = P.rotary_table({"base": 20000.0, "dims": 48})
-    assert ramped[0] == plain[0] and abs(ramped[-1] - plain[-1] / 4.0) < 1e-15 and any(
-        p / 4.0 < r < p for r, p in zip(ramped, plain))          # untouched, fully scaled, and in between
+    ramped, _ = P.rotary_table({"base": 30000.0, "dims": 40, "scaling": {"factor": 3.0, "original": 96, "fast": 24.0, "slow": 1.5}})
+    plain, _ = P.rotary_table({"base": 30000.0, "dims": 40})
+    assert ramped[0] == plain[0] and abs(ramped[-1] - plain[-1] / 3.0) < 1e-15 and any(
+        p / 3.0 * 1.0001 < r < p * 0.9999 for r, p in zip(ramped, plain))          # untouched, fully scaled, and in between
 
 
 def test_the_oracle_feels_every_mechanism(tmp_path):

@@ -68,7 +68,7 @@ CASE_B = model(64, 150, [lightning(1, 32, 32, (0.97,)),
                          attention(2, 2, 32, 16, 0.3, chunk=33, kv_from=2, mlp=None)], ff=40, alpha=1.0, eps=1e-5)
 # chunks of exactly one page and of exactly one key; a delta layer first; seven taps; keys wider than values
 CASE_C = model(80, 90, [delta(3, 3, 8, 16, 7),
-                        attention(2, 1, 48, 16, 0.3, chunk=64, rot_dims=48, base=20000.0, scaling=(4.0, 128, 32.0, 1.0)),
+                        attention(2, 1, 40, 16, 0.3, chunk=64, rot_dims=40, base=30000.0, scaling=(3.0, 96, 24.0, 1.5)),
                         attention(4, 4, 8, 8, 1.5, chunk=1, rot_dims=2),
                         lightning(4, 16, 8, (0.2, 0.7, 1.0, 0.999))], ff=24, alpha=0.6, emb_scale=0.5)
 # sizes that are multiples of nothing (a width of 100 is no multiple of 8: the tensor-core products step aside)
