@@ -305,6 +305,38 @@ def test_wider_layers_and_a_longer_prompt(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_first_tokens_at_the_tensor_core_kernels_sizes(folders, dtype):
+    """Requests of one and two tokens at head sizes that the tensor-core kernels take: a single token at position 0
+    (the single-token kernel), two short prompts side by side (the FMA kernel), then both decoded, then a prompt of
+    nine tokens beside them."""
+    vocab = CASES["E"][0]["vocab"]
+    seqs = [tokens(150, 12, vocab), tokens(151, 14, vocab), tokens(152, 9, vocab)]
+    want = _oracle(folders["E"], seqs)
+    r = _runner(folders["E"], dtype)
+    (a,) = r.admit(1)
+    got_a = [r.step([a], [seqs[0][:1]]).cpu()]
+    (b,) = r.admit(1)
+    out = r.step([b, a], [seqs[1][:2], seqs[0][1:3]], [[0, 1], [0, 1]]).cpu()
+    got_b, got_a = [out[:2]], got_a + [out[2:]]
+    for k in range(9):
+        out = r.step([a, b], [[seqs[0][3 + k]], [seqs[1][2 + k]]]).cpu()
+        got_a.append(out[0:1])
+        got_b.append(out[1:2])
+    (c,) = r.admit(1)
+    out = r.step([c, b], [seqs[2], seqs[1][11:14]], [list(range(9)), [0, 1, 2]]).cpu()
+    got_b.append(out[9:])
+    for g, x in ((torch.cat(got_a), want[0]), (torch.cat(got_b), want[1]), (out[:9], want[2])):
+        if dtype == "float32":
+            e = row_errors(g, x)
+            assert float(e.max()) <= 1e-4, f"worst {float(e.max()):.2e}"
+        else:
+            assert_rows(g, x, dtype, "first tokens")
+    for s_ in (a, b, c):
+        r.release(s_)
+    r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_engine(folders, dtype):
     """The public entry point and its scheduler: more prompts than run side by side, unequal lengths."""
     from plain import vagonex_plain as P
