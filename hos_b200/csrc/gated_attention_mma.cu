@@ -211,6 +211,8 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
 // query heads that share the kv head (up to 16); the four warps take a quarter of every tile's 64 keys each, with a
 // running maximum and sum of their own, and are merged through shared memory at the end.  With several shares the
 // merged (maximum, sum, weighted values) go to the workspace that attn_merge adds up.
+constexpr int kDecStages = 3;       // key/value tiles in flight per CTA
+
 template <int KD, int VD>
 __global__ void __launch_bounds__(128)
 gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
@@ -222,7 +224,7 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
     pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [16][KD]
-    bf16* kv_s = q_s + 16 * KD;                                    // stage s: K [64][KD] then V [64][VD]
+    bf16* kv_s = q_s + 16 * KD;                                    // kDecStages stages: K [64][KD] then V [64][VD]
     constexpr int kStage = MK * (KD + VD);
     const int n = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int QH = H / G, h0 = kvh * QH;
@@ -274,8 +276,10 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
         for (int i = threadIdx.x; i < MK * (KD / 8); i += 128) cp16(ks + i * 8, ksrc + i * 8);
         for (int i = threadIdx.x; i < MK * (VD / 8); i += 128) cp16(vs + i * 8, vsrc + i * 8);
     };
-    load_kv(kt_lo, 0);
-    cp_commit();
+    for (int s = 0; s < kDecStages - 1; ++s) {                      // the first tiles are on their way before anything else
+        if (s < n_kt) load_kv(kt_lo + s, s);
+        cp_commit();
+    }
 
     // the sink counts once: in the first share's first warp
     const bool with_sink = sink != nullptr && split == 0 && warp == 0;
@@ -292,10 +296,10 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
     const uint32_t q_base = smem_u32(q_s);
 
     for (int it = 0; it < n_kt; ++it) {
-        const int stage = it & 1;
-        if (it + 1 < n_kt) load_kv(kt_lo + it + 1, stage ^ 1);
+        const int stage = it % kDecStages;
+        if (it + kDecStages - 1 < n_kt) load_kv(kt_lo + it + kDecStages - 1, (it + kDecStages - 1) % kDecStages);
         cp_commit();
-        cp_wait<1>();
+        cp_wait<kDecStages - 1>();
         __syncthreads();
         const uint32_t k_base = smem_u32(kv_s + (size_t)stage * kStage);
         const uint32_t v_base = k_base + 2 * MK * KD;
@@ -466,8 +470,8 @@ extern "C" int hos_gated_attn_mma_decode(const float* q, const void* k_pages, co
     const dim3 grid(N, G, n_splits);
 #define HOS_GAD(KDv, VDv)                                                                                            \
     do {                                                                                                             \
-        constexpr int smem = (16 * KDv + 2 * MK * (KDv + VDv)) * 2;                                                  \
-        static_assert(4 * 16 * (VDv + 2) * 4 <= 2 * MK * (KDv + VDv) * 2, "the merge fits the stages");             \
+        constexpr int smem = (16 * KDv + kDecStages * MK * (KDv + VDv)) * 2;                                         \
+        static_assert(4 * 16 * (VDv + 2) * 4 <= kDecStages * MK * (KDv + VDv) * 2, "the merge fits the stages");    \
         static bool attr_set = false;                                                                                \
         if (!attr_set) {                                                                                             \
             cudaFuncSetAttribute(gated_attn_mma_decode_kernel<KDv, VDv>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \

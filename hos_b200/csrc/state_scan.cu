@@ -44,13 +44,13 @@ __global__ void act_rows_kernel(float* __restrict__ x, long long ld, int cols, l
     *p = silu_precise(*p);
 }
 
-template <int DR, bool DELTA>
+template <int DR, int R, bool DELTA>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long long ld,
                   int aligned, const float* __restrict__ g, long long g_ld, const float* __restrict__ beta,
                   long long beta_ld, float* __restrict__ state, const int* __restrict__ token_pos,
                   const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
-                  float* __restrict__ out, int H, int Gk, int dim, int vdim, int R, int CC) {
+                  float* __restrict__ out, int H, int Gk, int dim, int vdim, int CC) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * CC;
@@ -157,6 +157,7 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                         d3 = fmaf(S[4 * i + 3], kk.w, d3);
                     }
                     float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
                     for (int o = 1; o < R; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                     u = bs[t] * (u - dot);
                 }
@@ -186,6 +187,7 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             for (int t = 0; t < kScanChunk; ++t) {
                 if (t >= nt) break;
                 float acc = part[t];
+#pragma unroll
                 for (int o = 1; o < R; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                 if (r == 0 && c < CC) os[t * CC + c] = acc;
             }
@@ -312,6 +314,8 @@ extern "C" int hos_state_scan(const float* q, const float* k, const float* v, lo
     const int DR = dim <= 16 ? 4 : (dim <= 256 ? 8 : (dim <= 512 ? 16 : 32));
     int R = 1;
     while (R * DR < dim) R <<= 1;
+    if (DR == 8 && R < 4) R = 4;          // the compiled shapes (rows beyond dim are zeros)
+    if (DR >= 16) R = 32;
     int CC = 256 / R;
     if (CC > vdim) CC = vdim;
     // single tokens and few (sequence, head) pairs: fewer columns to a block, so that the blocks fill the GPU (columns
@@ -325,20 +329,28 @@ extern "C" int hos_state_scan(const float* q, const float* k, const float* v, lo
     const dim3 grid(n_seqs, H, (vdim + CC - 1) / CC);
     const bool delta = beta != nullptr;
     if (smem > 200 * 1024) HOS_REFUSE("state_scan: heads of %d x %d do not fit a block's shared memory", dim, vdim);
-#define HOS_SCAN(DRv, DL)                                                                                            \
-    if (smem > 48 * 1024)                                                                                            \
-        cudaFuncSetAttribute(state_scan_kernel<DRv, DL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    launch_pdl(state_scan_kernel<DRv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, aligned, g, g_ld, beta, \
-               beta_ld, state, token_pos, token_seq, cu_seqlens, seq_slot, out, H, Gk, dim, vdim, R, CC)
-#define HOS_SCAN_D(DRv)                                                                                              \
+#define HOS_SCAN(DRv, Rv, DL)                                                                                        \
     do {                                                                                                             \
-        if (delta) { HOS_SCAN(DRv, true); }                                                                          \
-        else { HOS_SCAN(DRv, false); }                                                                                 \
+        if (smem > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(state_scan_kernel<DRv, Rv, DL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_pdl(state_scan_kernel<DRv, Rv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, aligned, g, g_ld, beta, \
+                   beta_ld, state, token_pos, token_seq, cu_seqlens, seq_slot, out, H, Gk, dim, vdim, CC);           \
     } while (0)
-    if (DR == 4) HOS_SCAN_D(4);
-    else if (DR == 8) HOS_SCAN_D(8);
-    else if (DR == 16) HOS_SCAN_D(16);
-    else HOS_SCAN_D(32);
+#define HOS_SCAN_D(DRv, Rv)                                                                                          \
+    do {                                                                                                             \
+        if (delta) HOS_SCAN(DRv, Rv, true);                                                                          \
+        else HOS_SCAN(DRv, Rv, false);                                                                               \
+    } while (0)
+    // the shapes that the choice of DR above can give: (4; 1, 2, 4), (8; 4 to 32), (16; 32), (32; 32)
+    if (DR == 4 && R == 1) HOS_SCAN_D(4, 1);
+    else if (DR == 4 && R == 2) HOS_SCAN_D(4, 2);
+    else if (DR == 4) HOS_SCAN_D(4, 4);
+    else if (DR == 8 && R <= 4) HOS_SCAN_D(8, 4);
+    else if (DR == 8 && R == 8) HOS_SCAN_D(8, 8);
+    else if (DR == 8 && R == 16) HOS_SCAN_D(8, 16);
+    else if (DR == 8) HOS_SCAN_D(8, 32);
+    else if (DR == 16) HOS_SCAN_D(16, 32);
+    else HOS_SCAN_D(32, 32);
 #undef HOS_SCAN_D
 #undef HOS_SCAN
     return check_launch("state_scan");
