@@ -311,6 +311,8 @@ extern "C" int hos_state_scan(const float* q, const float* k, const float* v, lo
     // short runs of rows per thread: a token's walk is a chain of dependent instructions (scale, dot, sum over the
     // runs, update, read-out, sum), and with few (sequence, head) pairs nothing else hides its latency; the sums over
     // 16 or 32 runs are shuffles
+    // (heads of 128 x 128, 2,048 tokens, decay / delta rule: 4 rows to a thread 477 / 628 us, 8 rows 459 / 598, 16 rows
+    // 584 / 679, 32 rows 900 / 961)
     const int DR = dim <= 16 ? 4 : (dim <= 256 ? 8 : (dim <= 512 ? 16 : 32));
     int R = 1;
     while (R * DR < dim) R <<= 1;
