@@ -30,9 +30,9 @@ struct PagedKV2 {            // keys [n_pages][n_kv][64][kd], values [n_pages][n
 
 __device__ __forceinline__ int table_entry(const PagedKV2& c, int lp) { return c.ring_pages > 0 ? lp % c.ring_pages : lp; }
 
-constexpr int kPrepPL = 16;       // a head of up to 32 * 16 numbers in a warp's registers
+constexpr int kPrepMaxPL = 16;    // a head of up to 32 * 16 numbers in a warp's registers
 
-template <typename TC>
+template <typename TC, int kPrepPL>
 __global__ void __launch_bounds__(128)
 qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias, const float* __restrict__ q_norm,
                const float* __restrict__ k_norm, float eps, const float* __restrict__ freq, int rot_dims, float magnitude,
@@ -326,16 +326,25 @@ extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const f
                            const int* page_table, int table_stride, int ring_pages, int N, int H, int G, int kd, int vd,
                            cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (kd <= 0 || kd > 32 * kPrepPL) HOS_REFUSE("qk_prep: heads of %d numbers are outside 1..%d", kd, 32 * kPrepPL);
+    if (kd <= 0 || kd > 32 * kPrepMaxPL) HOS_REFUSE("qk_prep: heads of %d numbers are outside 1..%d", kd, 32 * kPrepMaxPL);
     if (freq == nullptr) rot_dims = 0;
     if (rot_dims % 2 != 0 || rot_dims > kd) HOS_REFUSE("qk_prep: %d rotated numbers in heads of %d", rot_dims, kd);
     PagedKV2 c{k_pages, v_pages, page_table, table_stride, ring_pages, G, kd, vd};
-    if (cache_dtype == kBF16)
-        launch_pdl(qk_prep_kernel<bf16>, dim3(N), dim3(128), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq, rot_dims,
-                   magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd);
-    else
-        launch_pdl(qk_prep_kernel<float>, dim3(N), dim3(128), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq, rot_dims,
-                   magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd);
+#define HOS_QKP(TC, PL)                                                                                              \
+    launch_pdl(qk_prep_kernel<TC, PL>, dim3(N), dim3(128), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq, rot_dims, \
+               magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd)
+#define HOS_QKP_T(TC)                                                                                                \
+    do {                                                                                                             \
+        if (kd <= 32) HOS_QKP(TC, 1);                                                                                \
+        else if (kd <= 64) HOS_QKP(TC, 2);                                                                           \
+        else if (kd <= 128) HOS_QKP(TC, 4);                                                                          \
+        else if (kd <= 256) HOS_QKP(TC, 8);                                                                          \
+        else HOS_QKP(TC, 16);                                                                                        \
+    } while (0)
+    if (cache_dtype == kBF16) HOS_QKP_T(bf16);
+    else HOS_QKP_T(float);
+#undef HOS_QKP_T
+#undef HOS_QKP
     return check_launch("qk_prep");
 }
 
