@@ -47,7 +47,7 @@ __global__ void act_rows_kernel(float* __restrict__ x, long long ld, int cols, l
 template <int DR, int R, bool DELTA>
 __global__ void __launch_bounds__(256)
 state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long long ld,
-                  int aligned, const float* __restrict__ g, long long g_ld, const float* __restrict__ beta,
+                  int aligned, int act_in_walk, const float* __restrict__ g, long long g_ld, const float* __restrict__ beta,
                   long long beta_ld, float* __restrict__ state, const int* __restrict__ token_pos,
                   const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                   float* __restrict__ out, int H, int Gk, int dim, int vdim, int CC) {
@@ -145,6 +145,7 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                 const float4* q4 = (const float4*)(qs + t * dpad + r * (DR + kPad));
                 const float gt = gs[t];
                 float u = c < CC ? vs[t * CC + c] : 0.f;
+                if (!DELTA && act_in_walk) u = silu_precise(u);      // single tokens: the activation rides here
                 if (DELTA) {
                     float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;       // four chains, not one of DR links
 #pragma unroll
@@ -164,7 +165,11 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < DR / 4; ++i) {
-                    const float4 kk = k4[i], qq = q4[i];
+                    float4 kk = k4[i], qq = q4[i];
+                    if (!DELTA && act_in_walk) {
+                        kk = make_float4(silu_precise(kk.x), silu_precise(kk.y), silu_precise(kk.z), silu_precise(kk.w));
+                        qq = make_float4(silu_precise(qq.x), silu_precise(qq.y), silu_precise(qq.z), silu_precise(qq.w));
+                    }
                     if (DELTA) {
                         S[4 * i] = fmaf(kk.x, u, S[4 * i]);
                         S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);
@@ -214,10 +219,11 @@ constexpr int kMaxTaps = 16;
 // the first C = 2 Gk dim + H vdim columns; conv_state: [slots][taps - 1][C], row j the input taps - 1 - j tokens back.
 __global__ void __launch_bounds__(256)
 conv_prep_kernel(const float* __restrict__ raw, long long ld, const float* __restrict__ conv_w, int taps,
-                 const float* __restrict__ conv_state, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                 const float* conv_state,      // may be written through keep_here: neither is __restrict__
+                 const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                  const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
                  const int* __restrict__ seq_slot, float* __restrict__ act, float* __restrict__ beta_out,
-                 float* __restrict__ g_out, int H, int Gk, int dim, int vdim) {
+                 float* __restrict__ g_out, int H, int Gk, int dim, int vdim, float* keep_here) {
     pdl_enter();
     extern __shared__ float qk[];                // [2 Gk dim] after the activation
     __shared__ float inv_len[64];
@@ -236,6 +242,9 @@ conv_prep_kernel(const float* __restrict__ raw, long long ld, const float* __res
     const int r0 = cu_seqlens[seq];
     const bool fresh = token_pos[r0] == 0;
     const float* keep = conv_state + (size_t)seq_slot[seq] * (taps - 1) * C;
+    // keep_here: every sequence of the step brings one token, so this block alone reads and writes its slot's kept
+    // inputs (a thread the channels it convolves): they move on by one here instead of in a launch of their own
+    float* keep_w = keep_here != nullptr ? keep_here + (size_t)seq_slot[seq] * (taps - 1) * C : nullptr;
     for (int ch = threadIdx.x; ch < C; ch += blockDim.x) {
         float acc = 0.f;
         for (int j = 0; j < taps; ++j) {
@@ -244,6 +253,7 @@ conv_prep_kernel(const float* __restrict__ raw, long long ld, const float* __res
             if (src >= r0) x = raw[(size_t)src * ld + ch];
             else if (!fresh) x = keep[(size_t)((taps - 1) + (src - r0)) * C + ch];
             acc = fmaf(conv_w[(size_t)ch * taps + j], x, acc);
+            if (keep_w != nullptr && j >= 1) keep_w[(size_t)(j - 1) * C + ch] = x;      // row j - 1 is read before this
         }
         const float y = silu_precise(acc);
         if (ch < QK) qk[ch] = y;
@@ -300,8 +310,9 @@ using namespace hos;
 
 // q, k: rows of Gk heads of `dim` numbers; v: rows of H heads of `vdim`; all float32 with `ld` numbers between rows.
 // g: [.][H] with g_ld between rows (0: one row of constants).  beta: null for the decay rule.  state: [slots][H][vdim][dim].
-// out: float32 [N][H][vdim].
-extern "C" int hos_state_scan(const float* q, const float* k, const float* v, long long ld, const float* g,
+// out: float32 [N][H][vdim].  act_in_walk (decay rule only, meant for single-token steps): q, k, v are taken through
+// x logistic(x) as they are read, instead of by hos_act_rows before.
+extern "C" int hos_state_scan(const float* q, const float* k, const float* v, long long ld, int act_in_walk, const float* g,
                               long long g_ld, const float* beta, long long beta_ld, float* state, const int* token_pos,
                               const int* token_seq, const int* cu_seqlens, const int* seq_slot, float* out, int n_rows,
                               int n_seqs, int H, int Gk, int dim, int vdim, cudaStream_t stream) {
@@ -330,12 +341,13 @@ extern "C" int hos_state_scan(const float* q, const float* k, const float* v, lo
     const int aligned = (dim % 4 == 0 && ld % 4 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0) ? 1 : 0;
     const dim3 grid(n_seqs, H, (vdim + CC - 1) / CC);
     const bool delta = beta != nullptr;
+    if (delta && act_in_walk) HOS_REFUSE("state_scan: the activation in the walk is the decay rule's");
     if (smem > 200 * 1024) HOS_REFUSE("state_scan: heads of %d x %d do not fit a block's shared memory", dim, vdim);
 #define HOS_SCAN(DRv, Rv, DL)                                                                                        \
     do {                                                                                                             \
         if (smem > 48 * 1024)                                                                                        \
             cudaFuncSetAttribute(state_scan_kernel<DRv, Rv, DL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        launch_pdl(state_scan_kernel<DRv, Rv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, aligned, g, g_ld, beta, \
+        launch_pdl(state_scan_kernel<DRv, Rv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, aligned, act_in_walk, g, g_ld, beta, \
                    beta_ld, state, token_pos, token_seq, cu_seqlens, seq_slot, out, H, Gk, dim, vdim, CC);           \
     } while (0)
 #define HOS_SCAN_D(DRv, Rv)                                                                                          \
@@ -365,18 +377,21 @@ extern "C" int hos_act_rows(float* x, long long ld, int cols, int N, cudaStream_
     return check_launch("act_rows");
 }
 
+// keep_here: 1 only where every sequence of the step brings exactly one token: the kept inputs then move on inside this
+// launch and hos_conv_keep is not needed.
 // act: float32 [N][2 Gk dim + H vdim] (q, k, v after convolution, activation and lengths); beta_out, g_out: [N][H].
 extern "C" int hos_conv_prep(const float* raw, long long ld, const float* conv_w, int taps, const float* conv_state,
                              const float* a_log, const float* dt_bias, const int* token_pos, const int* token_seq,
                              const int* cu_seqlens, const int* seq_slot, float* act, float* beta_out, float* g_out, int N,
-                             int H, int Gk, int dim, int vdim, cudaStream_t stream) {
+                             int H, int Gk, int dim, int vdim, int keep_here, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (taps < 1 || taps > kMaxTaps) HOS_REFUSE("conv_prep: %d taps are outside 1..%d", taps, kMaxTaps);
     const size_t smem = (size_t)2 * Gk * dim * sizeof(float);
     if (smem > 160 * 1024) HOS_REFUSE("conv_prep: %d query and key channels do not fit", 2 * Gk * dim);
     if (smem > 48 * 1024) cudaFuncSetAttribute(conv_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(conv_prep_kernel, dim3(N), dim3(256), smem, stream, raw, ld, conv_w, taps, conv_state, a_log, dt_bias,
-               token_pos, token_seq, cu_seqlens, seq_slot, act, beta_out, g_out, H, Gk, dim, vdim);
+               token_pos, token_seq, cu_seqlens, seq_slot, act, beta_out, g_out, H, Gk, dim, vdim,
+               keep_here ? const_cast<float*>(conv_state) : (float*)nullptr);
     return check_launch("conv_prep");
 }
 

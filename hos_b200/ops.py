@@ -888,12 +888,13 @@ def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_l
     if out.shape != (n, heads * vdim) or tuple(state.shape[1:]) != (heads, vdim, dim):
         raise KernelError("state_scan: sizes disagree")
     base = rows.data_ptr()
-    if silu_on_load:        # q, k, v lie side by side from q_col on: x logistic(x) in place, once, before the walk
+    in_walk = bool(silu_on_load) and beta is None and step.max_new == 1      # single tokens: no launch of its own for it
+    if silu_on_load and not in_walk:        # q, k, v lie side by side from q_col on: x logistic(x) in place, once, before the walk
         if not (q_col < k_col < v_col) or v_col + heads * vdim - q_col != 2 * key_heads * dim + heads * vdim:
             raise KernelError("state_scan: q, k, v must lie side by side for the activation")
         mixers().call("hos_act_rows", ctypes.c_void_p(base + 4 * q_col), ld, 2 * key_heads * dim + heads * vdim, n, _stream())
     mixers().call("hos_state_scan", ctypes.c_void_p(base + 4 * q_col), ctypes.c_void_p(base + 4 * k_col),
-                  ctypes.c_void_p(base + 4 * v_col), ld, _ptr(g), heads if per_token_g else 0,
+                  ctypes.c_void_p(base + 4 * v_col), ld, 1 if in_walk else 0, _ptr(g), heads if per_token_g else 0,
                   _ptr(beta), heads if beta is not None else 0, _ptr(state), _ptr(step.token_pos), _ptr(step.token_seq),
                   _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out), n, int(step.n_seqs), int(heads), int(key_heads),
                   int(dim), int(vdim), _stream())
@@ -901,8 +902,9 @@ def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_l
 
 def conv_prep(raw: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
               step, act: torch.Tensor, beta: torch.Tensor, g: torch.Tensor, heads: int, key_heads: int, dim: int,
-              vdim: int) -> None:
-    """raw: float32 [N, ld] = [q | k | v | b | a | ...] projections; conv_w: [C, taps]; conv_state: [slots, taps - 1, C]."""
+              vdim: int, keep_here: bool = False) -> None:
+    """raw: float32 [N, ld] = [q | k | v | b | a | ...] projections; conv_w: [C, taps]; conv_state: [slots, taps - 1, C].
+    keep_here (only where every sequence brings one token): the kept inputs move on in this launch, conv_keep is not needed."""
     _check(raw, "projection rows", torch.float32, 2)
     _check(conv_w, "convolution weights", torch.float32, 2)
     n, c = raw.shape[0], 2 * key_heads * dim + heads * vdim
@@ -912,7 +914,7 @@ def conv_prep(raw: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor,
         raise KernelError("conv_prep: sizes disagree")
     mixers().call("hos_conv_prep", _ptr(raw), raw.shape[1], _ptr(conv_w), taps, _ptr(conv_state), _ptr(a_log), _ptr(dt_bias),
                   _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(act),
-                  _ptr(beta), _ptr(g), n, int(heads), int(key_heads), int(dim), int(vdim), _stream())
+                  _ptr(beta), _ptr(g), n, int(heads), int(key_heads), int(dim), int(vdim), 1 if keep_here else 0, _stream())
 
 
 def conv_keep(raw: torch.Tensor, taps: int, conv_state: torch.Tensor, step, channels: int) -> None:

@@ -140,9 +140,11 @@ class GatedDeltaRule(Mixer):
         beta = torch.empty((n, self.n_heads), dtype=torch.float32, device=dev)
         g = torch.empty((n, self.n_heads), dtype=torch.float32, device=dev)
         kept = store.state["conv"]
+        single = step.max_new == 1           # every sequence brings one token: the kept inputs move on in conv_prep itself
         ops.conv_prep(raw, self.conv_w, kept, self.a_log, self.dt_bias, step, act, beta, g, self.n_heads, self.n_kv_heads,
-                      self.dim, self.vdim)
-        ops.conv_keep(raw, self.taps, kept, step, self.conv_cols)
+                      self.dim, self.vdim, keep_here=single)
+        if not single:
+            ops.conv_keep(raw, self.taps, kept, step, self.conv_cols)
         o = torch.empty((n, self.v_cols), dtype=torch.float32, device=dev)
         ops.state_scan(act, 0, self.qk_cols, 2 * self.qk_cols, False, g, True, beta, store.state["S"], step, o,
                        self.n_heads, self.n_kv_heads, self.dim, self.vdim)
