@@ -14,6 +14,7 @@ step must read (every weight once, and the cache of the live sequences) to its t
 
 `--design satapel` (or `vagonex`) is another measurement (not the line above): prompt and decode throughput of that design at
 a few sizes beside Gemma-2 at equal size, and each of the design's kernels against its roofline; one JSON line per size.
+With `--profile prefill|decode` it measures nothing and runs two such steps of one block of layers kernel by kernel, for a profiler.
 
 Random weights are made on the device; the cache of the decode measurements is filled with
 random keys and values instead of being computed by a prompt (a decode step reads the same

@@ -465,7 +465,7 @@ def test_the_kernels_alone_against_float64():
         tot = [a + b for a, b in zip(lens, starts)]
         n2 = sum(lens)
         q2 = torch.randn(n2, H, kd2, device=dev)
-        pages_of, table, nxt = [], torch.zeros(3, 4, dtype=torch.int32), 1
+        table, nxt = torch.zeros(3, 4, dtype=torch.int32), 1
         for sq, t in enumerate(tot):
             for e in range((t + 63) // 64):
                 table[sq, e] = nxt
@@ -474,8 +474,6 @@ def test_the_kernels_alone_against_float64():
         vp2 = torch.zeros(nxt + 1, G, 64, vd2, device=dev, dtype=torch.bfloat16)
         ks = [torch.randn(t, G, kd2).to(torch.bfloat16) for t in tot]
         vs = [torch.randn(t, G, vd2).to(torch.bfloat16) for t in tot]
-        from hos_b200.parts.gated_attention import GatedSoftmaxAttention  # noqa: F401  (the layout helper below is the cache's)
-
         def place(pages, rows, hd):
             for sq, r in enumerate(rows):
                 for t in range(r.shape[0]):
